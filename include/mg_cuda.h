@@ -1,0 +1,189 @@
+/*
+ * mg_cuda.h — C ABI of the B200 (sm_100a) device backend for micrograd's fp64
+ * tensor-op path.
+ *
+ * The reference project has no FFI for this path: its ops are loops inside the
+ * C++ `Tensor` methods (src/ops/*.cpp, src/core/*.cpp).  This header is the
+ * boundary those method bodies are replaced by.  Each entry point names the
+ * reference loop it stands in for.  All pointers named `d_*`, and every
+ * `double *` / `int *` argument unless marked "host", are DEVICE pointers
+ * obtained from mg_alloc(); tensors are dense, row-major, fp64.
+ *
+ * Conventions
+ *   - Every function returns MG_OK (0) or a negative MG_ERR_* code and never
+ *     throws; mg_last_error() returns a thread-local description.
+ *   - Work is enqueued on one ordered compute stream per process and returns
+ *     without waiting; only mg_download*, mg_sync, mg_event_elapsed_ms and the
+ *     bounded waits block the host.
+ *   - One device per process (one process per GPU).  mg_init() is implicit: the
+ *     first call that needs the device initialises it from MG_DEVICE, else
+ *     LOCAL_RANK, else device 0.  There is no CPU fallback: without a usable
+ *     CUDA device every call fails with MG_ERR_CUDA.
+ *   - Backward entry points ACCUMULATE (`+=`), like the reference's closures.
+ *     `flags` bit MG_ACC_STORE_A / _B says the destination gradient is known to
+ *     be all zero, so the kernel may store instead of read-modify-write; the
+ *     result is the same value.
+ */
+#ifndef MG_CUDA_H
+#define MG_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MG_OK 0
+#define MG_ERR_INVALID (-1) /* bad argument                                */
+#define MG_ERR_OOM (-2)     /* device allocation failed                    */
+#define MG_ERR_CUDA (-3)    /* CUDA runtime / driver error, or no device   */
+#define MG_ERR_NCCL (-4)    /* NCCL error                                  */
+#define MG_ERR_TIMEOUT (-5) /* a bounded wait expired                      */
+#define MG_ERR_KERNEL (-6)  /* a kernel reported an internal fault flag    */
+
+#define MG_ACC_STORE_A 1 /* first gradient destination is known zero  */
+#define MG_ACC_STORE_B 2 /* second gradient destination is known zero */
+
+/* ---- lifecycle -------------------------------------------------------- */
+/* Role of the reference's MetalContext singleton
+ * (src/metal/MetalContext.cpp:9-63): device, queue, buffers. */
+const char *mg_last_error(void);
+int mg_init(int device); /* device < 0: MG_DEVICE, LOCAL_RANK, then 0 */
+int mg_shutdown(void);
+int mg_device(void); /* current device ordinal, -1 before init */
+int mg_sm_count(void);
+int mg_sync(void);                 /* wait for the compute and comm streams */
+int mg_check_kernel_status(void);  /* MG_ERR_KERNEL if a kernel raised its fault flag (syncs) */
+int mg_mem_info(size_t *free_bytes, size_t *total_bytes);
+
+/* ---- storage ----------------------------------------------------------- */
+/* Replaces std::vector<double> data_/grad_ (include/micrograd/Tensor.h:55-56,
+ * src/core/Tensor.cpp:7-28).  Stream-ordered: memory freed here may be handed
+ * to a later mg_alloc and is safe for work enqueued after that call. */
+int mg_alloc(size_t n, double **out);
+int mg_free(double *p);
+int mg_alloc_i32(size_t n, int **out);
+int mg_free_i32(int *p);
+int mg_upload(double *dst, const double *src_host, size_t n);   /* pageable or pinned host */
+int mg_download(double *dst_host, const double *src, size_t n); /* blocks until done */
+int mg_upload_i32(int *dst, const int *src_host, size_t n);
+int mg_download_i32(int *dst_host, const int *src, size_t n);
+int mg_fill(double *dst, double value, size_t n); /* Tensor.cpp:12-13, 73-77; Autograd.cpp:23-25 */
+int mg_copy(double *dst, const double *src, size_t n);
+/* Pinned host staging memory for callers that stream batches in. */
+int mg_host_alloc(size_t bytes, void **out_host);
+int mg_host_free(void *host);
+
+/* ---- elementwise, tensor (x) tensor: src/ops/Arithmetic.cpp:9-135 ------ */
+enum { MG_ADD = 0, MG_SUB = 1, MG_MUL = 2, MG_DIV = 3 };
+int mg_binary_fwd(int op, const double *a, const double *b, double *out, size_t n);
+/* ga/gb may be NULL (skipped) and may alias each other (x op x). */
+int mg_binary_bwd(int op, const double *a, const double *b, const double *g, double *ga,
+                  double *gb, size_t n, int flags);
+
+/* ---- elementwise, tensor (x) scalar and unary -------------------------- */
+/* Arithmetic.cpp:137-266 (scalar add/sub/mul/div, pow) and
+ * src/ops/Activations.cpp:8-88 (relu, sigmoid, tanh).  MG_EXP has no
+ * counterpart in the reference (forward exp(x), backward g*out). */
+enum {
+  MG_SADD = 0, MG_SSUB = 1, MG_SMUL = 2, MG_SDIV = 3, MG_POW = 4,
+  MG_RELU = 5, MG_SIGMOID = 6, MG_TANH = 7, MG_EXP = 8
+};
+int mg_unary_fwd(int op, const double *a, double s, double *out, size_t n);
+/* `a` = forward input, `out` = forward output (used by sigmoid/tanh/exp). */
+int mg_unary_bwd(int op, const double *a, const double *out, double s, const double *g,
+                 double *ga, size_t n, int flags);
+
+/* ---- row broadcast (no counterpart in the reference; the batched form of
+ * Linear::forward's bias add, src/nn.cpp:55-57) --------------------------- */
+int mg_add_row_fwd(const double *x, const double *row, double *out, size_t M, size_t N);
+/* gx[M,N] += g ; grow[N] += column sums of g.  Either may be NULL. */
+int mg_add_row_bwd(const double *g, double *gx, double *grow, size_t M, size_t N, int flags);
+
+/* ---- reductions --------------------------------------------------------- */
+/* Full sum: src/ops/Reduction.cpp:17-21 (forward), :26-30 (backward, the
+ * scalar g[0] is read on the device).  Fixed-shape two-level tree, so the
+ * result does not depend on the run. */
+int mg_sum_all_fwd(const double *x, double *out1, size_t n);
+int mg_sum_all_bwd(const double *g1, double *gx, size_t n, int flags);
+/* Last-axis sum [M,N] -> [M] (no counterpart in the reference). */
+int mg_sum_lastaxis_fwd(const double *x, double *out, size_t M, size_t N);
+int mg_sum_lastaxis_bwd(const double *g, double *gx, size_t M, size_t N, int flags);
+
+/* ---- matmul: src/ops/Matmul.cpp ----------------------------------------- */
+enum { MG_EPI_NONE = 0, MG_EPI_BIAS = 1, MG_EPI_BIAS_RELU = 2, MG_EPI_RELU_MASK = 3 };
+/* Forward, Matmul.cpp:30-38: C[M,N] (+)= A[M,K] . B[K,N].
+ * epilogue MG_EPI_BIAS adds bias[N] to every row, MG_EPI_BIAS_RELU also applies
+ * max(.,0) (fused Linear::forward + relu). */
+int mg_gemm_nn(const double *A, const double *B, double *C, size_t M, size_t N, size_t K,
+               int accumulate, int epilogue, const double *bias);
+/* dA, Matmul.cpp:44-50: dA[M,K] (+)= G[M,N] . B[K,N]^T.
+ * epilogue MG_EPI_RELU_MASK multiplies element (i,j) by (mask_src[i,j] > 0)
+ * before it is accumulated (the relu backward of Activations.cpp:25-30 fused). */
+int mg_gemm_nt(const double *G, const double *B, double *dA, size_t M, size_t N, size_t K,
+               int accumulate, int epilogue, const double *mask_src);
+/* dB, Matmul.cpp:52-58: dB[K,N] (+)= A[M,K]^T . G[M,N]. */
+int mg_gemm_tn(const double *A, const double *G, double *dB, size_t M, size_t N, size_t K,
+               int accumulate);
+
+/* Diagnostic knob for tests and benchmarks.  path: 0 automatic choice, 1 plain
+ * tiled kernel only, 2 tensor-core kernel whenever the operands allow it.
+ * dmma_shape: -1 default, else the mma.sync f64 shape as in
+ * mg_probe_dmma_tflops(). */
+int mg_gemm_config(int path, int dmma_shape);
+
+/* ---- fused loss / prediction (no counterpart in the reference) ---------- */
+/* Softmax cross-entropy over rows of logits[M,C] with class ids labels[M]
+ * (int).  loss1[0] = sum_i loss_i / denom; denom is the global batch size so a
+ * row shard produces its share of the global mean. */
+int mg_softmax_xent_fwd(const double *logits, const int *labels, double *loss1, size_t M,
+                        size_t C, double denom);
+/* glogits[M,C] += gloss1[0] * (softmax - onehot) / denom. */
+int mg_softmax_xent_bwd(const double *logits, const int *labels, const double *gloss1,
+                        double *glogits, size_t M, size_t C, double denom, int flags);
+/* First index of the strict row maximum (the `>` loop of src/main.cpp:29-32). */
+int mg_argmax_rows(const double *x, int *out, size_t M, size_t N);
+/* labels stored as doubles -> int class ids. */
+int mg_f64_to_i32(const double *src, int *dst, size_t n);
+
+/* ---- optimiser: src/nn.cpp:65-77 ----------------------------------------- */
+int mg_sgd_step(double *param, const double *grad, double lr, size_t n); /* p -= (lr*g) */
+
+/* ---- events / timing on the compute stream ------------------------------ */
+int mg_event_create(int *out_id);
+int mg_event_record(int id);
+int mg_event_elapsed_ms(int start_id, int stop_id, float *ms); /* syncs on stop */
+int mg_event_destroy(int id);
+/* Host wait with a deadline: MG_ERR_TIMEOUT if the event has not completed. */
+int mg_event_wait_bounded(int id, double timeout_s);
+
+/* ---- data-parallel communication (no counterpart in the reference) ------ */
+/* NCCL over NVLink.  The all-reduce runs on a separate comm stream, ordered
+ * after everything enqueued on the compute stream so far; the compute stream
+ * does not wait for it until mg_comm_join(). */
+int mg_comm_unique_id(char *out128_host);
+int mg_comm_init(const char *id128_host, int rank, int world);
+int mg_comm_destroy(void);
+int mg_comm_rank(void);
+int mg_comm_world(void);
+int mg_allreduce_sum_async(double *buf, size_t n);
+int mg_comm_join(void); /* compute stream waits for all all-reduces enqueued so far */
+/* Polls NCCL's async error state and the comm stream up to timeout_s; aborts
+ * the communicator and returns MG_ERR_TIMEOUT / MG_ERR_NCCL on failure. */
+int mg_comm_wait_bounded(double timeout_s);
+
+/* ---- measurement helpers -------------------------------------------------- */
+/* Issue-rate probe of the FP64 tensor-core instruction (mma.sync ... f64) with
+ * register operands only; writes achieved TFLOP/s.  shape: 0 m8n8k4, 1 m16n8k4,
+ * 2 m16n8k8, 3 m16n8k16. */
+int mg_probe_dmma_tflops(int shape, int iters, double *tflops_host);
+/* Overwrites a buffer larger than L2 so the next timed launch starts cold. */
+int mg_flush_l2(void);
+/* Count of kernel launches issued by this library since process start. */
+unsigned long long mg_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MG_CUDA_H */

@@ -89,9 +89,15 @@ void mgt_free_str(char *s);
 #ifdef MG_B200_EXTENSIONS
 /* ---- additive API of the B200 backend (no counterpart in the reference) ---- */
 mgt_tensor mgt_sum_axis(mgt_tensor a, int axis);
-mgt_tensor mgt_softmax_cross_entropy(mgt_tensor logits, mgt_tensor labels);
+/* denom: divisor of the mean; 0 = number of rows. */
+mgt_tensor mgt_softmax_cross_entropy(mgt_tensor logits, mgt_tensor labels, double denom);
 /* labels_host: nrows class ids; uploads them inside the call. */
-mgt_tensor mgt_softmax_cross_entropy_host(mgt_tensor logits, const int *labels_host, size_t nrows);
+mgt_tensor mgt_softmax_cross_entropy_host(mgt_tensor logits, const int *labels_host, size_t nrows,
+                                          double denom);
+/* Tensor::from_host: uploads straight from caller memory (pinned or pageable). */
+mgt_tensor mgt_new_from_host(const size_t *shape, size_t ndim, const double *values);
+int mgt_comm_rank(void);
+int mgt_comm_world(void);
 int mgt_argmax_rows(mgt_tensor x, int *out, size_t nrows);
 mgt_tensor mgt_linear_forward_relu(mgt_linear l, mgt_tensor input);
 int mgt_set_requires_grad(mgt_tensor t, int flag);

@@ -1,0 +1,94 @@
+#pragma once
+// Device-resident fp64 buffer with a lazily materialised host mirror.
+//
+// Stands in for the reference's `std::vector<double> data_, grad_`
+// (include/micrograd/Tensor.h:55-56).  The authoritative copy is in GPU memory;
+// a host std::vector appears only when the public accessors data()/grad()/at()
+// ask for one.  Those accessors hand out mutable references, so once the host
+// view has been lent the device copy is treated as stale and is refreshed from
+// the host vector before the next kernel touches it.
+
+#include <cstddef>
+#include <memory>
+#include <vector>
+
+namespace micrograd::detail {
+
+class Storage {
+public:
+  Storage() = default;
+  ~Storage();
+  Storage(const Storage &) = delete;
+  Storage &operator=(const Storage &) = delete;
+
+  // Logical all-zero contents of `n` elements; nothing is allocated yet.
+  void init_zero(size_t n);
+  // Takes ownership of host values and uploads them.
+  void init_from_host(std::vector<double> &&values);
+  // Uploads `n` values straight from caller memory (may be pinned).
+  void init_from_pointer(const double *values, size_t n);
+
+  size_t size() const { return size_; }
+  bool is_zero() const { return zero_; }
+
+  // Device pointer whose contents are current; for kernels that only read.
+  const double *device_read();
+  // Device pointer the caller will overwrite completely.
+  double *device_overwrite();
+  // Device pointer for `+=`.  If the contents are logically zero, *store is set
+  // and the caller must write every element instead of accumulating.
+  double *device_accumulate(bool *store);
+  // Device pointer for in-place update of current contents.
+  double *device_update();
+
+  void set_zero();          // back to logical zeros (keeps any buffer)
+  void fill(double value);  // every element := value, on the device
+
+  // Host views.  The mutable one marks the device copy stale.
+  std::vector<double> &host_mutable();
+  const std::vector<double> &host_const();
+  double peek(size_t index);  // one element, without lending the host view
+
+  // Moves the contents into caller-owned device memory (a slice of a flat
+  // parameter/gradient buffer) and uses that memory from now on.
+  // `keepalive` owns that memory.
+  void rehome(double *slice, std::shared_ptr<void> keepalive);
+  // True when the device buffer holds the current values (not logical zeros,
+  // not superseded by a lent host view).
+  bool device_current() const { return !zero_ && dev_valid_; }
+
+private:
+  void ensure_device_buffer();
+  void sync_device_from_host();
+  void sync_host_from_device();
+
+  size_t size_ = 0;
+  double *dev_ = nullptr;
+  bool owns_dev_ = true;
+  std::shared_ptr<void> keepalive_;
+  bool zero_ = true;         // logically all zeros; dev_/host_ contents irrelevant
+  bool dev_valid_ = false;   // dev_ holds the current values
+  bool host_valid_ = false;  // host_ holds the current values
+  std::vector<double> host_;
+};
+
+// Device-side int buffer (class ids), shared by graph closures.
+class DeviceInts {
+public:
+  DeviceInts(const int *host_values, size_t n);
+  explicit DeviceInts(size_t n);
+  ~DeviceInts();
+  DeviceInts(const DeviceInts &) = delete;
+  DeviceInts &operator=(const DeviceInts &) = delete;
+  int *get() const { return dev_; }
+  size_t size() const { return n_; }
+
+private:
+  int *dev_ = nullptr;
+  size_t n_ = 0;
+};
+
+// Throws std::runtime_error carrying mg_last_error() when rc != 0.
+void check(int rc, const char *what);
+
+}  // namespace micrograd::detail

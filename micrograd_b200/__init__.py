@@ -10,8 +10,8 @@ The product is two shared libraries built in-tree by ``micrograd_b200.build``:
   (``include/micrograd/*.h``) as a thin graph-building layer over that ABI, plus
   the flat C binding ``include/mg_tensor_c.h``.
 
-Python is only the test and benchmark harness: ``cabi()`` gives ctypes access
-to the device C ABI, ``api()`` a mirror of the C++ classes.  There is no CPU
+Python is only the test and benchmark harness: ``load_abi()`` gives ctypes access
+to the device C ABI, ``load_api()`` a mirror of the C++ classes.  There is no CPU
 fallback: both raise if the libraries are missing, and every device entry
 point fails with an error if no CUDA device can be initialised.
 """
@@ -28,7 +28,7 @@ _api = None
 _cabi = None
 
 
-def api():
+def load_api():
     """Python mirror of the C++ Tensor / Linear / SGD API (B200 backend)."""
     global _api
     if _api is None:
@@ -39,7 +39,7 @@ def api():
     return _api
 
 
-def cabi():
+def load_abi():
     """ctypes view of the device C ABI (include/mg_cuda.h)."""
     global _cabi
     if _cabi is None:

@@ -1,0 +1,87 @@
+// Shared host-side plumbing of the device backend: the per-process context
+// (device, streams, scratch), error reporting and launch-geometry helpers.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstddef>
+#include <cstdint>
+#include <cstdio>
+
+#include "mg_cuda.h"
+
+namespace mg {
+
+// Number of partial sums the two-level reductions use.  Fixed (not derived from
+// the device) so that a sum has the same association order on every run.
+constexpr int kReducePartials = 1184;  // 148 SMs x 8
+constexpr int kReduceThreads = 256;
+
+struct Context {
+  bool ready = false;
+  int device = -1;
+  int sm_count = 0;
+  cudaStream_t stream = nullptr;       // compute stream (ordered)
+  cudaStream_t comm_stream = nullptr;  // NCCL all-reduces
+  cudaEvent_t fork_event = nullptr;    // compute -> comm ordering
+  cudaEvent_t join_event = nullptr;    // comm -> compute ordering
+  // Scratch for reductions: partial sums and the "blocks done" ticket.
+  double *reduce_partials = nullptr;   // kReducePartials doubles (x2 for row/col use)
+  unsigned int *reduce_ticket = nullptr;
+  // Column-sum scratch (add_row backward, bias gradients): [kColSplit][N].
+  double *colsum_scratch = nullptr;
+  size_t colsum_scratch_elems = 0;
+  // Split-K scratch for the transposed-A GEMM.
+  double *splitk_scratch = nullptr;
+  size_t splitk_scratch_elems = 0;
+  // Kernel fault word: kernels write a non-zero code here instead of trapping.
+  int *kernel_status = nullptr;        // device
+  // L2 flush buffer.
+  void *flush_buf = nullptr;
+  size_t flush_bytes = 0;
+  unsigned long long launches = 0;
+};
+
+Context &ctx();
+int ensure_init();
+
+// Records a formatted message for mg_last_error() and returns `code`.
+int fail(int code, const char *fmt, ...);
+int cuda_fail(cudaError_t e, const char *what);
+
+// Grows a scratch buffer (stream-ordered free + alloc) to at least `elems`.
+int ensure_scratch(double **buf, size_t *have, size_t elems);
+
+inline void count_launch() { ctx().launches++; }
+
+#define MG_CUDA_TRY(expr)                                                                          \
+  do {                                                                                             \
+    cudaError_t mg_e_ = (expr);                                                                    \
+    if (mg_e_ != cudaSuccess) return ::mg::cuda_fail(mg_e_, #expr);                                \
+  } while (0)
+
+#define MG_ENSURE_INIT()                                                                           \
+  do {                                                                                             \
+    int mg_rc_ = ::mg::ensure_init();                                                              \
+    if (mg_rc_ != MG_OK) return mg_rc_;                                                            \
+  } while (0)
+
+#define MG_LAUNCH_CHECK(name)                                                                      \
+  do {                                                                                             \
+    ::mg::count_launch();                                                                          \
+    cudaError_t mg_e_ = cudaGetLastError();                                                        \
+    if (mg_e_ != cudaSuccess) return ::mg::cuda_fail(mg_e_, name);                                 \
+  } while (0)
+
+// Grid for a grid-stride kernel over `work_items` with `threads` per CTA:
+// enough CTAs to cover the work, capped at `ctas_per_sm` resident CTAs per SM
+// so the grid is a whole number of waves on the 148-SM part.
+inline unsigned grid_for(size_t work_items, int threads, int ctas_per_sm) {
+  size_t need = (work_items + (size_t)threads - 1) / (size_t)threads;
+  size_t cap = (size_t)ctx().sm_count * (size_t)ctas_per_sm;
+  if (need < 1) need = 1;
+  return (unsigned)(need < cap ? need : cap);
+}
+
+}  // namespace mg

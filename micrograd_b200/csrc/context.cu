@@ -1,0 +1,353 @@
+// Lifecycle, storage, events: the parts of the C ABI that hold no arithmetic.
+#include "common.cuh"
+
+#include <chrono>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
+namespace mg {
+
+namespace {
+thread_local std::string t_last_error;
+std::mutex g_init_mutex;
+Context g_ctx;
+std::vector<cudaEvent_t> g_events;
+}  // namespace
+
+Context &ctx() { return g_ctx; }
+
+int fail(int code, const char *fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  t_last_error = buf;
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char *what) {
+  int code = (e == cudaErrorMemoryAllocation) ? MG_ERR_OOM : MG_ERR_CUDA;
+  return fail(code, "CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+}
+
+static int pick_device() {
+  const char *names[] = {"MG_DEVICE", "LOCAL_RANK"};
+  for (const char *n : names) {
+    const char *v = std::getenv(n);
+    if (v && *v) return std::atoi(v);
+  }
+  return 0;
+}
+
+static int init_locked(int device) {
+  Context &c = g_ctx;
+  if (c.ready) {
+    if (device >= 0 && device != c.device)
+      return fail(MG_ERR_INVALID, "mg_init: already bound to device %d (one device per process)",
+                  c.device);
+    return MG_OK;
+  }
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0) {
+    return fail(MG_ERR_CUDA,
+                "no usable CUDA device (%s); this backend has no CPU fallback",
+                e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0");
+  }
+  if (device < 0) device = pick_device();
+  if (device >= count)
+    return fail(MG_ERR_INVALID, "device %d requested but only %d visible", device, count);
+  MG_CUDA_TRY(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  MG_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+  c.device = device;
+  c.sm_count = prop.multiProcessorCount;
+  MG_CUDA_TRY(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
+  MG_CUDA_TRY(cudaStreamCreateWithFlags(&c.comm_stream, cudaStreamNonBlocking));
+  MG_CUDA_TRY(cudaEventCreateWithFlags(&c.fork_event, cudaEventDisableTiming));
+  MG_CUDA_TRY(cudaEventCreateWithFlags(&c.join_event, cudaEventDisableTiming));
+  // Keep freed blocks in the stream-ordered pool instead of returning them to
+  // the driver: op results are allocated and freed every step.
+  cudaMemPool_t pool;
+  MG_CUDA_TRY(cudaDeviceGetDefaultMemPool(&pool, device));
+  uint64_t threshold = UINT64_MAX;
+  MG_CUDA_TRY(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &threshold));
+  MG_CUDA_TRY(cudaMalloc(&c.reduce_partials, sizeof(double) * 2 * kReducePartials));
+  MG_CUDA_TRY(cudaMalloc(&c.reduce_ticket, sizeof(unsigned int) * 4));
+  MG_CUDA_TRY(cudaMemset(c.reduce_ticket, 0, sizeof(unsigned int) * 4));
+  MG_CUDA_TRY(cudaMalloc(&c.kernel_status, sizeof(int)));
+  MG_CUDA_TRY(cudaMemset(c.kernel_status, 0, sizeof(int)));
+  MG_CUDA_TRY(cudaDeviceSynchronize());
+  c.ready = true;
+  return MG_OK;
+}
+
+int ensure_init() {
+  if (g_ctx.ready) return MG_OK;
+  std::lock_guard<std::mutex> lock(g_init_mutex);
+  return init_locked(-1);
+}
+
+int ensure_scratch(double **buf, size_t *have, size_t elems) {
+  if (*have >= elems) return MG_OK;
+  Context &c = ctx();
+  if (*buf) MG_CUDA_TRY(cudaFreeAsync(*buf, c.stream));
+  *buf = nullptr;
+  *have = 0;
+  MG_CUDA_TRY(cudaMallocAsync(buf, elems * sizeof(double), c.stream));
+  *have = elems;
+  return MG_OK;
+}
+
+}  // namespace mg
+
+using namespace mg;
+
+extern "C" {
+
+const char *mg_last_error(void) { return t_last_error.c_str(); }
+
+int mg_init(int device) {
+  std::lock_guard<std::mutex> lock(g_init_mutex);
+  return init_locked(device);
+}
+
+int mg_shutdown(void) {
+  std::lock_guard<std::mutex> lock(g_init_mutex);
+  Context &c = g_ctx;
+  if (!c.ready) return MG_OK;
+  cudaDeviceSynchronize();
+  for (cudaEvent_t ev : g_events)
+    if (ev) cudaEventDestroy(ev);
+  g_events.clear();
+  if (c.colsum_scratch) cudaFreeAsync(c.colsum_scratch, c.stream);
+  if (c.splitk_scratch) cudaFreeAsync(c.splitk_scratch, c.stream);
+  cudaStreamSynchronize(c.stream);
+  cudaFree(c.reduce_partials);
+  cudaFree(c.reduce_ticket);
+  cudaFree(c.kernel_status);
+  if (c.flush_buf) cudaFree(c.flush_buf);
+  cudaEventDestroy(c.fork_event);
+  cudaEventDestroy(c.join_event);
+  cudaStreamDestroy(c.stream);
+  cudaStreamDestroy(c.comm_stream);
+  unsigned long long launches = c.launches;
+  c = Context();
+  c.launches = launches;
+  return MG_OK;
+}
+
+int mg_device(void) { return g_ctx.ready ? g_ctx.device : -1; }
+
+int mg_sm_count(void) {
+  if (ensure_init() != MG_OK) return 0;
+  return g_ctx.sm_count;
+}
+
+int mg_sync(void) {
+  MG_ENSURE_INIT();
+  MG_CUDA_TRY(cudaStreamSynchronize(g_ctx.stream));
+  MG_CUDA_TRY(cudaStreamSynchronize(g_ctx.comm_stream));
+  return MG_OK;
+}
+
+int mg_check_kernel_status(void) {
+  MG_ENSURE_INIT();
+  int status = 0;
+  MG_CUDA_TRY(cudaMemcpyAsync(&status, g_ctx.kernel_status, sizeof(int), cudaMemcpyDeviceToHost,
+                              g_ctx.stream));
+  MG_CUDA_TRY(cudaStreamSynchronize(g_ctx.stream));
+  if (status != 0) {
+    cudaMemsetAsync(g_ctx.kernel_status, 0, sizeof(int), g_ctx.stream);
+    return fail(MG_ERR_KERNEL, "a kernel raised fault code %d (bounded wait expired or bad geometry)",
+                status);
+  }
+  return MG_OK;
+}
+
+int mg_mem_info(size_t *free_bytes, size_t *total_bytes) {
+  MG_ENSURE_INIT();
+  MG_CUDA_TRY(cudaMemGetInfo(free_bytes, total_bytes));
+  return MG_OK;
+}
+
+/* ---- storage ---- */
+
+static int alloc_bytes(size_t bytes, void **out) {
+  MG_ENSURE_INIT();
+  if (!out) return fail(MG_ERR_INVALID, "mg_alloc: null out pointer");
+  if (bytes == 0) bytes = 16;
+  void *p = nullptr;
+  cudaError_t e = cudaMallocAsync(&p, bytes, g_ctx.stream);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(e == cudaErrorMemoryAllocation ? MG_ERR_OOM : MG_ERR_CUDA,
+                "device allocation of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+  }
+  *out = p;
+  return MG_OK;
+}
+
+int mg_alloc(size_t n, double **out) { return alloc_bytes(n * sizeof(double), (void **)out); }
+int mg_alloc_i32(size_t n, int **out) { return alloc_bytes(n * sizeof(int), (void **)out); }
+
+int mg_free(double *p) {
+  if (!p) return MG_OK;
+  if (!g_ctx.ready) return MG_OK;  // after shutdown the pool is gone with the context
+  MG_CUDA_TRY(cudaFreeAsync(p, g_ctx.stream));
+  return MG_OK;
+}
+
+int mg_free_i32(int *p) { return mg_free(reinterpret_cast<double *>(p)); }
+
+int mg_upload(double *dst, const double *src_host, size_t n) {
+  MG_ENSURE_INIT();
+  if (n == 0) return MG_OK;
+  if (!dst || !src_host) return fail(MG_ERR_INVALID, "mg_upload: null pointer");
+  MG_CUDA_TRY(cudaMemcpyAsync(dst, src_host, n * sizeof(double), cudaMemcpyHostToDevice,
+                              g_ctx.stream));
+  return MG_OK;
+}
+
+int mg_download(double *dst_host, const double *src, size_t n) {
+  MG_ENSURE_INIT();
+  if (n == 0) return MG_OK;
+  if (!dst_host || !src) return fail(MG_ERR_INVALID, "mg_download: null pointer");
+  MG_CUDA_TRY(cudaMemcpyAsync(dst_host, src, n * sizeof(double), cudaMemcpyDeviceToHost,
+                              g_ctx.stream));
+  MG_CUDA_TRY(cudaStreamSynchronize(g_ctx.stream));
+  return MG_OK;
+}
+
+int mg_upload_i32(int *dst, const int *src_host, size_t n) {
+  MG_ENSURE_INIT();
+  if (n == 0) return MG_OK;
+  if (!dst || !src_host) return fail(MG_ERR_INVALID, "mg_upload_i32: null pointer");
+  MG_CUDA_TRY(cudaMemcpyAsync(dst, src_host, n * sizeof(int), cudaMemcpyHostToDevice,
+                              g_ctx.stream));
+  return MG_OK;
+}
+
+int mg_download_i32(int *dst_host, const int *src, size_t n) {
+  MG_ENSURE_INIT();
+  if (n == 0) return MG_OK;
+  if (!dst_host || !src) return fail(MG_ERR_INVALID, "mg_download_i32: null pointer");
+  MG_CUDA_TRY(cudaMemcpyAsync(dst_host, src, n * sizeof(int), cudaMemcpyDeviceToHost,
+                              g_ctx.stream));
+  MG_CUDA_TRY(cudaStreamSynchronize(g_ctx.stream));
+  return MG_OK;
+}
+
+int mg_copy(double *dst, const double *src, size_t n) {
+  MG_ENSURE_INIT();
+  if (n == 0) return MG_OK;
+  if (!dst || !src) return fail(MG_ERR_INVALID, "mg_copy: null pointer");
+  MG_CUDA_TRY(cudaMemcpyAsync(dst, src, n * sizeof(double), cudaMemcpyDeviceToDevice,
+                              g_ctx.stream));
+  return MG_OK;
+}
+
+int mg_host_alloc(size_t bytes, void **out_host) {
+  MG_ENSURE_INIT();
+  if (!out_host) return fail(MG_ERR_INVALID, "mg_host_alloc: null out pointer");
+  MG_CUDA_TRY(cudaMallocHost(out_host, bytes ? bytes : 16));
+  return MG_OK;
+}
+
+int mg_host_free(void *host) {
+  if (!host) return MG_OK;
+  MG_CUDA_TRY(cudaFreeHost(host));
+  return MG_OK;
+}
+
+/* ---- events ---- */
+
+int mg_event_create(int *out_id) {
+  MG_ENSURE_INIT();
+  if (!out_id) return fail(MG_ERR_INVALID, "mg_event_create: null out pointer");
+  cudaEvent_t ev;
+  MG_CUDA_TRY(cudaEventCreate(&ev));
+  for (size_t i = 0; i < g_events.size(); i++) {
+    if (!g_events[i]) {
+      g_events[i] = ev;
+      *out_id = (int)i;
+      return MG_OK;
+    }
+  }
+  g_events.push_back(ev);
+  *out_id = (int)g_events.size() - 1;
+  return MG_OK;
+}
+
+static int event_at(int id, cudaEvent_t *ev) {
+  if (id < 0 || (size_t)id >= g_events.size() || !g_events[id])
+    return fail(MG_ERR_INVALID, "unknown event id %d", id);
+  *ev = g_events[id];
+  return MG_OK;
+}
+
+int mg_event_record(int id) {
+  MG_ENSURE_INIT();
+  cudaEvent_t ev;
+  int rc = event_at(id, &ev);
+  if (rc != MG_OK) return rc;
+  MG_CUDA_TRY(cudaEventRecord(ev, g_ctx.stream));
+  return MG_OK;
+}
+
+int mg_event_elapsed_ms(int start_id, int stop_id, float *ms) {
+  MG_ENSURE_INIT();
+  cudaEvent_t a, b;
+  int rc = event_at(start_id, &a);
+  if (rc != MG_OK) return rc;
+  rc = event_at(stop_id, &b);
+  if (rc != MG_OK) return rc;
+  MG_CUDA_TRY(cudaEventSynchronize(b));
+  MG_CUDA_TRY(cudaEventElapsedTime(ms, a, b));
+  return MG_OK;
+}
+
+int mg_event_destroy(int id) {
+  cudaEvent_t ev;
+  int rc = event_at(id, &ev);
+  if (rc != MG_OK) return rc;
+  cudaEventDestroy(ev);
+  g_events[id] = nullptr;
+  return MG_OK;
+}
+
+int mg_event_wait_bounded(int id, double timeout_s) {
+  MG_ENSURE_INIT();
+  cudaEvent_t ev;
+  int rc = event_at(id, &ev);
+  if (rc != MG_OK) return rc;
+  auto deadline = std::chrono::steady_clock::now() + std::chrono::duration<double>(timeout_s);
+  for (;;) {
+    cudaError_t e = cudaEventQuery(ev);
+    if (e == cudaSuccess) return MG_OK;
+    if (e != cudaErrorNotReady) return cuda_fail(e, "cudaEventQuery");
+    if (std::chrono::steady_clock::now() >= deadline)
+      return fail(MG_ERR_TIMEOUT, "event %d not complete after %.3f s", id, timeout_s);
+    std::this_thread::sleep_for(std::chrono::microseconds(50));
+  }
+}
+
+unsigned long long mg_launch_count(void) { return g_ctx.launches; }
+
+int mg_flush_l2(void) {
+  MG_ENSURE_INIT();
+  Context &c = g_ctx;
+  if (!c.flush_buf) {
+    c.flush_bytes = (size_t)256 << 20;  // 256 MiB, twice the 126 MB L2
+    MG_CUDA_TRY(cudaMalloc(&c.flush_buf, c.flush_bytes));
+  }
+  MG_CUDA_TRY(cudaMemsetAsync(c.flush_buf, 0, c.flush_bytes, c.stream));
+  return MG_OK;
+}
+
+}  // extern "C"

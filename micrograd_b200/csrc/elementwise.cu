@@ -1,0 +1,493 @@
+// Elementwise forward/backward kernels, row-broadcast add, SGD update, fill.
+//
+// All of these are HBM-bound streaming kernels: one generic grid-stride "map"
+// kernel moves 16-byte vectors (two doubles) with four independent vectors in
+// flight per thread, and a small functor supplies the arithmetic.  The grid is
+// a whole number of waves (SM count x resident CTAs), each thread striding
+// through the array so that consecutive threads touch consecutive 16-byte
+// words.
+//
+// This file is compiled with -fmad=false: the reference rounds every multiply
+// and add separately (it is built without FMA contraction), and add, sub, mul,
+// relu, their gradients and the SGD update are bit-identical to it only if the
+// device does the same.
+#include "common.cuh"
+
+namespace mg {
+
+constexpr int kEwThreads = 256;
+constexpr int kEwUnroll = 4;
+constexpr int kEwCtasPerSm = 8;
+
+template <int VEC> struct VecT;
+template <> struct VecT<2> {
+  using type = double2;
+  static __device__ __forceinline__ double2 zero() { return make_double2(0.0, 0.0); }
+};
+template <> struct VecT<1> {
+  using type = double;
+  static __device__ __forceinline__ double zero() { return 0.0; }
+};
+
+__device__ __forceinline__ double lane(const double &v, int) { return v; }
+__device__ __forceinline__ double lane(const double2 &v, int i) { return i == 0 ? v.x : v.y; }
+__device__ __forceinline__ void set_lane(double &v, int, double x) { v = x; }
+__device__ __forceinline__ void set_lane(double2 &v, int i, double x) {
+  if (i == 0) v.x = x; else v.y = x;
+}
+
+// Streaming loads/stores: every element is touched once, so keep it out of L1.
+template <class V> __device__ __forceinline__ V ld_stream(const V *p) { return __ldcs(p); }
+template <class V> __device__ __forceinline__ void st_stream(V *p, V v) { __stcs(p, v); }
+
+// F provides: static constexpr int NI, NO; const double *in[NI]; double *out[NO];
+// __device__ void compute(const double (&i)[NI], double (&o)[NO]) const.
+// A null in[k] reads as 0.0 without touching memory; a null out[k] is skipped.
+template <int VEC, class F>
+__global__ void __launch_bounds__(kEwThreads) map_kernel(F f, size_t n) {
+  using V = typename VecT<VEC>::type;
+  constexpr int NI = F::NI, NO = F::NO;
+  const size_t nvec = n / VEC;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+
+  auto process = [&](const V(&v)[NI > 0 ? NI : 1], size_t at) {
+    V o[NO];
+#pragma unroll
+    for (int l = 0; l < VEC; l++) {
+      double si[NI > 0 ? NI : 1], so[NO];
+#pragma unroll
+      for (int k = 0; k < NI; k++) si[k] = lane(v[k], l);
+      f.compute(si, so);
+#pragma unroll
+      for (int k = 0; k < NO; k++) set_lane(o[k], l, so[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < NO; k++)
+      if (f.out[k]) st_stream(reinterpret_cast<V *>(f.out[k]) + at, o[k]);
+  };
+
+  // Main loop: kEwUnroll independent vectors per thread; all loads are issued
+  // before the first store so they overlap.
+  for (; i + (kEwUnroll - 1) * stride < nvec; i += kEwUnroll * stride) {
+    V v[kEwUnroll][NI > 0 ? NI : 1];
+#pragma unroll
+    for (int u = 0; u < kEwUnroll; u++) {
+#pragma unroll
+      for (int k = 0; k < NI; k++)
+        v[u][k] = f.in[k] ? ld_stream(reinterpret_cast<const V *>(f.in[k]) + i + u * stride)
+                          : VecT<VEC>::zero();
+    }
+#pragma unroll
+    for (int u = 0; u < kEwUnroll; u++) process(v[u], i + u * stride);
+  }
+  for (; i < nvec; i += stride) {
+    V v[NI > 0 ? NI : 1];
+#pragma unroll
+    for (int k = 0; k < NI; k++)
+      v[k] = f.in[k] ? ld_stream(reinterpret_cast<const V *>(f.in[k]) + i) : VecT<VEC>::zero();
+    process(v, i);
+  }
+  // Odd tail element of the vector path.
+  if (VEC == 2 && (n & 1) && blockIdx.x == 0 && threadIdx.x == 0) {
+    double si[NI > 0 ? NI : 1], so[NO];
+#pragma unroll
+    for (int k = 0; k < NI; k++) si[k] = f.in[k] ? f.in[k][n - 1] : 0.0;
+    f.compute(si, so);
+#pragma unroll
+    for (int k = 0; k < NO; k++)
+      if (f.out[k]) f.out[k][n - 1] = so[k];
+  }
+}
+
+template <class F> static bool all_aligned16(const F &f) {
+  uintptr_t bits = 0;
+  for (int k = 0; k < F::NI; k++) bits |= reinterpret_cast<uintptr_t>(f.in[k]);
+  for (int k = 0; k < F::NO; k++) bits |= reinterpret_cast<uintptr_t>(f.out[k]);
+  return (bits & 15) == 0;
+}
+
+template <class F> static int launch_map(const F &f, size_t n, const char *name) {
+  if (n == 0) return MG_OK;
+  Context &c = ctx();
+  if (all_aligned16(f)) {
+    unsigned grid = grid_for((n + 1) / 2, kEwThreads, kEwCtasPerSm);
+    map_kernel<2, F><<<grid, kEwThreads, 0, c.stream>>>(f, n);
+  } else {
+    unsigned grid = grid_for(n, kEwThreads, kEwCtasPerSm);
+    map_kernel<1, F><<<grid, kEwThreads, 0, c.stream>>>(f, n);
+  }
+  MG_LAUNCH_CHECK(name);
+  return MG_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Functors
+// ---------------------------------------------------------------------------
+template <int OP> struct BinaryFwd {
+  static constexpr int NI = 2, NO = 1;
+  const double *in[NI];
+  double *out[NO];
+  __device__ __forceinline__ void compute(const double (&i)[NI], double (&o)[NO]) const {
+    if (OP == MG_ADD) o[0] = i[0] + i[1];
+    else if (OP == MG_SUB) o[0] = i[0] - i[1];
+    else if (OP == MG_MUL) o[0] = i[0] * i[1];
+    else o[0] = i[0] / i[1];
+  }
+};
+
+// in: g, a, b, old ga, old gb.  out: ga, gb.  Null "old" pointers read as 0, which
+// turns the accumulation into a plain store of the same value.
+template <int OP> struct BinaryBwd {
+  static constexpr int NI = 5, NO = 2;
+  const double *in[NI];
+  double *out[NO];
+  __device__ __forceinline__ void compute(const double (&i)[NI], double (&o)[NO]) const {
+    const double g = i[0], a = i[1], b = i[2];
+    if (OP == MG_ADD) {
+      o[0] = i[3] + g;
+      o[1] = i[4] + g;
+    } else if (OP == MG_SUB) {
+      o[0] = i[3] + g;
+      o[1] = i[4] - g;
+    } else if (OP == MG_MUL) {
+      o[0] = i[3] + g * b;
+      o[1] = i[4] + g * a;
+    } else {
+      o[0] = i[3] + g / b;
+      o[1] = i[4] - (g * a) / (b * b);
+    }
+  }
+};
+
+template <int OP> struct UnaryFwd {
+  static constexpr int NI = 1, NO = 1;
+  const double *in[NI];
+  double *out[NO];
+  double s;
+  __device__ __forceinline__ void compute(const double (&i)[NI], double (&o)[NO]) const {
+    const double x = i[0];
+    if (OP == MG_SADD) o[0] = x + s;
+    else if (OP == MG_SSUB) o[0] = x - s;
+    else if (OP == MG_SMUL) o[0] = x * s;
+    else if (OP == MG_SDIV) o[0] = x / s;
+    else if (OP == MG_POW) o[0] = pow(x, s);
+    else if (OP == MG_RELU) o[0] = x > 0 ? x : 0.0;
+    else if (OP == MG_SIGMOID) o[0] = 1.0 / (1.0 + exp(-x));
+    else if (OP == MG_TANH) o[0] = tanh(x);
+    else o[0] = exp(x);
+  }
+};
+
+// in: g, a (forward input), y (forward output), old ga.  out: ga.
+template <int OP> struct UnaryBwd {
+  static constexpr int NI = 4, NO = 1;
+  const double *in[NI];
+  double *out[NO];
+  double s;
+  __device__ __forceinline__ void compute(const double (&i)[NI], double (&o)[NO]) const {
+    const double g = i[0], a = i[1], y = i[2], old = i[3];
+    if (OP == MG_SADD || OP == MG_SSUB) o[0] = old + g;
+    else if (OP == MG_SMUL) o[0] = old + g * s;
+    else if (OP == MG_SDIV) o[0] = old + g / s;
+    else if (OP == MG_POW) o[0] = old + (g * s) * pow(a, s - 1.0);
+    else if (OP == MG_RELU) o[0] = old + g * (a > 0 ? 1.0 : 0.0);
+    else if (OP == MG_SIGMOID) o[0] = old + (g * y) * (1.0 - y);
+    else if (OP == MG_TANH) o[0] = old + g * (1.0 - y * y);
+    else o[0] = old + g * y;
+  }
+};
+
+struct FillFn {
+  static constexpr int NI = 0, NO = 1;
+  const double *in[1];
+  double *out[NO];
+  double value;
+  __device__ __forceinline__ void compute(const double (&)[1], double (&o)[NO]) const {
+    o[0] = value;
+  }
+};
+
+// in: p, g.  out: p.  p - (lr*g) with the product rounded first (src/nn.cpp:74).
+struct SgdFn {
+  static constexpr int NI = 2, NO = 1;
+  const double *in[NI];
+  double *out[NO];
+  double lr;
+  __device__ __forceinline__ void compute(const double (&i)[NI], double (&o)[NO]) const {
+    o[0] = i[0] - lr * i[1];
+  }
+};
+
+// ---------------------------------------------------------------------------
+// Row-broadcast add: out[r, c] = x[r, c] + row[c].  Each thread owns a flat
+// 16-byte word and advances (r, c) incrementally, so the loop has no division.
+// ---------------------------------------------------------------------------
+template <int VEC>
+__global__ void __launch_bounds__(kEwThreads)
+add_row_kernel(const double *__restrict__ x, const double *__restrict__ row,
+               double *__restrict__ out, size_t M, size_t N) {
+  using V = typename VecT<VEC>::type;
+  const size_t ncol = N / VEC;  // vectors per row
+  const size_t total = M * ncol;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t drow = stride / ncol, dcol = stride % ncol;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t c = i % ncol;
+  const V *xv = reinterpret_cast<const V *>(x);
+  const V *rv = reinterpret_cast<const V *>(row);
+  V *ov = reinterpret_cast<V *>(out);
+  (void)drow;
+  for (; i < total; i += stride) {
+    V a = ld_stream(xv + i);
+    V b = __ldg(rv + c);
+    V o;
+#pragma unroll
+    for (int l = 0; l < VEC; l++) set_lane(o, l, lane(a, l) + lane(b, l));
+    st_stream(ov + i, o);
+    c += dcol;
+    if (c >= ncol) c -= ncol;
+  }
+}
+
+
+// sum() backward: gx[i] += g[0], the scalar read from device memory
+// (src/ops/Reduction.cpp:26-30).  in: old gx.  out: gx.
+struct ScalarBroadcastBwd {
+  static constexpr int NI = 1, NO = 1;
+  const double *in[NI];
+  double *out[NO];
+  const double *g0;
+  __device__ __forceinline__ void compute(const double (&i)[NI], double (&o)[NO]) const {
+    o[0] = i[0] + __ldg(g0);
+  }
+};
+
+// Last-axis-sum backward: gx[r, c] += g[r].
+template <int VEC>
+__global__ void __launch_bounds__(kEwThreads)
+row_scalar_bwd_kernel(const double *__restrict__ g, double *__restrict__ gx, size_t M, size_t N,
+                      bool accumulate) {
+  using V = typename VecT<VEC>::type;
+  const size_t ncol = N / VEC;
+  const size_t total = M * ncol;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t drow = stride / ncol, dcol = stride % ncol;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t r = i / ncol, c = i % ncol;
+  V *gv = reinterpret_cast<V *>(gx);
+  for (; i < total; i += stride) {
+    const double s = __ldg(g + r);
+    V o = accumulate ? ld_stream(gv + i) : VecT<VEC>::zero();
+#pragma unroll
+    for (int l = 0; l < VEC; l++) set_lane(o, l, lane(o, l) + s);
+    st_stream(gv + i, o);
+    c += dcol;
+    r += drow;
+    if (c >= ncol) {
+      c -= ncol;
+      r++;
+    }
+  }
+}
+
+__global__ void f64_to_i32_kernel(const double *__restrict__ src, int *__restrict__ dst, size_t n) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    dst[i] = (int)src[i];
+}
+
+}  // namespace mg
+
+using namespace mg;
+
+// Dispatch a runtime op code to the functor template.
+#define MG_DISPATCH_BINARY(OPVAR, CALL)                                                            \
+  switch (OPVAR) {                                                                                 \
+    case MG_ADD: { constexpr int OP = MG_ADD; CALL; } break;                                       \
+    case MG_SUB: { constexpr int OP = MG_SUB; CALL; } break;                                       \
+    case MG_MUL: { constexpr int OP = MG_MUL; CALL; } break;                                       \
+    case MG_DIV: { constexpr int OP = MG_DIV; CALL; } break;                                       \
+    default: return fail(MG_ERR_INVALID, "unknown binary op %d", OPVAR);                           \
+  }
+
+#define MG_DISPATCH_UNARY(OPVAR, CALL)                                                             \
+  switch (OPVAR) {                                                                                 \
+    case MG_SADD: { constexpr int OP = MG_SADD; CALL; } break;                                     \
+    case MG_SSUB: { constexpr int OP = MG_SSUB; CALL; } break;                                     \
+    case MG_SMUL: { constexpr int OP = MG_SMUL; CALL; } break;                                     \
+    case MG_SDIV: { constexpr int OP = MG_SDIV; CALL; } break;                                     \
+    case MG_POW: { constexpr int OP = MG_POW; CALL; } break;                                       \
+    case MG_RELU: { constexpr int OP = MG_RELU; CALL; } break;                                     \
+    case MG_SIGMOID: { constexpr int OP = MG_SIGMOID; CALL; } break;                               \
+    case MG_TANH: { constexpr int OP = MG_TANH; CALL; } break;                                     \
+    case MG_EXP: { constexpr int OP = MG_EXP; CALL; } break;                                       \
+    default: return fail(MG_ERR_INVALID, "unknown unary op %d", OPVAR);                            \
+  }
+
+template <int OP>
+static int binary_bwd_one(const double *a, const double *b, const double *g, double *ga, double *gb,
+                          size_t n, int flags) {
+  BinaryBwd<OP> f;
+  const bool needs_ab = (OP == MG_MUL || OP == MG_DIV);
+  f.in[0] = g;
+  f.in[1] = needs_ab ? a : nullptr;
+  f.in[2] = needs_ab ? b : nullptr;
+  f.in[3] = (ga && !(flags & MG_ACC_STORE_A)) ? ga : nullptr;
+  f.in[4] = (gb && !(flags & MG_ACC_STORE_B)) ? gb : nullptr;
+  f.out[0] = ga;
+  f.out[1] = gb;
+  return launch_map(f, n, "binary_bwd");
+}
+
+extern "C" {
+
+int mg_fill(double *dst, double value, size_t n) {
+  MG_ENSURE_INIT();
+  if (n == 0) return MG_OK;
+  if (!dst) return fail(MG_ERR_INVALID, "mg_fill: null pointer");
+  if (value == 0.0) {  // +0.0 is all-zero bits
+    MG_CUDA_TRY(cudaMemsetAsync(dst, 0, n * sizeof(double), ctx().stream));
+    return MG_OK;
+  }
+  FillFn f;
+  f.in[0] = nullptr;
+  f.out[0] = dst;
+  f.value = value;
+  return launch_map(f, n, "fill");
+}
+
+int mg_binary_fwd(int op, const double *a, const double *b, double *out, size_t n) {
+  MG_ENSURE_INIT();
+  if (n && (!a || !b || !out)) return fail(MG_ERR_INVALID, "mg_binary_fwd: null pointer");
+  int rc = MG_OK;
+  MG_DISPATCH_BINARY(op, {
+    BinaryFwd<OP> f;
+    f.in[0] = a; f.in[1] = b; f.out[0] = out;
+    rc = launch_map(f, n, "binary_fwd");
+  });
+  return rc;
+}
+
+int mg_binary_bwd(int op, const double *a, const double *b, const double *g, double *ga,
+                  double *gb, size_t n, int flags) {
+  MG_ENSURE_INIT();
+  if (n == 0 || (!ga && !gb)) return MG_OK;
+  if (!g) return fail(MG_ERR_INVALID, "mg_binary_bwd: null upstream gradient");
+  if ((op == MG_MUL || op == MG_DIV) && (!a || !b))
+    return fail(MG_ERR_INVALID, "mg_binary_bwd: mul/div need both forward operands");
+  int rc = MG_OK;
+  if (ga && ga == gb) {
+    // Both operands are one tensor: apply the two updates one after the other,
+    // in the reference's order (first operand, then second).
+    MG_DISPATCH_BINARY(op, {
+      rc = binary_bwd_one<OP>(a, b, g, ga, nullptr, n, flags & MG_ACC_STORE_A);
+      if (rc == MG_OK) rc = binary_bwd_one<OP>(a, b, g, nullptr, gb, n, 0);
+    });
+    return rc;
+  }
+  MG_DISPATCH_BINARY(op, { rc = binary_bwd_one<OP>(a, b, g, ga, gb, n, flags); });
+  return rc;
+}
+
+int mg_unary_fwd(int op, const double *a, double s, double *out, size_t n) {
+  MG_ENSURE_INIT();
+  if (n && (!a || !out)) return fail(MG_ERR_INVALID, "mg_unary_fwd: null pointer");
+  int rc = MG_OK;
+  MG_DISPATCH_UNARY(op, {
+    UnaryFwd<OP> f;
+    f.in[0] = a; f.out[0] = out; f.s = s;
+    rc = launch_map(f, n, "unary_fwd");
+  });
+  return rc;
+}
+
+int mg_unary_bwd(int op, const double *a, const double *out, double s, const double *g,
+                 double *ga, size_t n, int flags) {
+  MG_ENSURE_INIT();
+  if (n == 0 || !ga) return MG_OK;
+  if (!g) return fail(MG_ERR_INVALID, "mg_unary_bwd: null upstream gradient");
+  const bool needs_a = (op == MG_POW || op == MG_RELU);
+  const bool needs_y = (op == MG_SIGMOID || op == MG_TANH || op == MG_EXP);
+  if ((needs_a && !a) || (needs_y && !out))
+    return fail(MG_ERR_INVALID, "mg_unary_bwd: op %d needs its forward %s", op,
+                needs_a ? "input" : "output");
+  int rc = MG_OK;
+  MG_DISPATCH_UNARY(op, {
+    UnaryBwd<OP> f;
+    f.in[0] = g;
+    f.in[1] = needs_a ? a : nullptr;
+    f.in[2] = needs_y ? out : nullptr;
+    f.in[3] = (flags & MG_ACC_STORE_A) ? nullptr : ga;
+    f.out[0] = ga;
+    f.s = s;
+    rc = launch_map(f, n, "unary_bwd");
+  });
+  return rc;
+}
+
+int mg_sgd_step(double *param, const double *grad, double lr, size_t n) {
+  MG_ENSURE_INIT();
+  if (n == 0) return MG_OK;
+  if (!param || !grad) return fail(MG_ERR_INVALID, "mg_sgd_step: null pointer");
+  SgdFn f;
+  f.in[0] = param; f.in[1] = grad; f.out[0] = param; f.lr = lr;
+  return launch_map(f, n, "sgd_step");
+}
+
+int mg_add_row_fwd(const double *x, const double *row, double *out, size_t M, size_t N) {
+  MG_ENSURE_INIT();
+  if (M == 0 || N == 0) return MG_OK;
+  if (!x || !row || !out) return fail(MG_ERR_INVALID, "mg_add_row_fwd: null pointer");
+  Context &c = ctx();
+  uintptr_t bits = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(row) |
+                   reinterpret_cast<uintptr_t>(out);
+  if ((N % 2 == 0) && (bits & 15) == 0) {
+    unsigned grid = grid_for(M * (N / 2), kEwThreads, kEwCtasPerSm);
+    add_row_kernel<2><<<grid, kEwThreads, 0, c.stream>>>(x, row, out, M, N);
+  } else {
+    unsigned grid = grid_for(M * N, kEwThreads, kEwCtasPerSm);
+    add_row_kernel<1><<<grid, kEwThreads, 0, c.stream>>>(x, row, out, M, N);
+  }
+  MG_LAUNCH_CHECK("add_row_fwd");
+  return MG_OK;
+}
+
+int mg_sum_all_bwd(const double *g1, double *gx, size_t n, int flags) {
+  MG_ENSURE_INIT();
+  if (n == 0 || !gx) return MG_OK;
+  if (!g1) return fail(MG_ERR_INVALID, "mg_sum_all_bwd: null upstream gradient");
+  ScalarBroadcastBwd f;
+  f.in[0] = (flags & MG_ACC_STORE_A) ? nullptr : gx;
+  f.out[0] = gx;
+  f.g0 = g1;
+  return launch_map(f, n, "sum_all_bwd");
+}
+
+int mg_sum_lastaxis_bwd(const double *g, double *gx, size_t M, size_t N, int flags) {
+  MG_ENSURE_INIT();
+  if (M == 0 || N == 0 || !gx) return MG_OK;
+  if (!g) return fail(MG_ERR_INVALID, "mg_sum_lastaxis_bwd: null upstream gradient");
+  Context &c = ctx();
+  const bool acc = !(flags & MG_ACC_STORE_A);
+  if ((N % 2 == 0) && (reinterpret_cast<uintptr_t>(gx) & 15) == 0) {
+    unsigned grid = grid_for(M * (N / 2), kEwThreads, kEwCtasPerSm);
+    row_scalar_bwd_kernel<2><<<grid, kEwThreads, 0, c.stream>>>(g, gx, M, N, acc);
+  } else {
+    unsigned grid = grid_for(M * N, kEwThreads, kEwCtasPerSm);
+    row_scalar_bwd_kernel<1><<<grid, kEwThreads, 0, c.stream>>>(g, gx, M, N, acc);
+  }
+  MG_LAUNCH_CHECK("sum_lastaxis_bwd");
+  return MG_OK;
+}
+
+int mg_f64_to_i32(const double *src, int *dst, size_t n) {
+  MG_ENSURE_INIT();
+  if (n == 0) return MG_OK;
+  if (!src || !dst) return fail(MG_ERR_INVALID, "mg_f64_to_i32: null pointer");
+  f64_to_i32_kernel<<<grid_for(n, 256, 4), 256, 0, ctx().stream>>>(src, dst, n);
+  MG_LAUNCH_CHECK("f64_to_i32");
+  return MG_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,594 @@
+// fp64 matrix multiply: forward C = A.B (src/ops/Matmul.cpp:30-38) and the two
+// gradient products dA += G.B^T (:44-50) and dB += A^T.G (:52-58).
+//
+// Main kernel: FP64 tensor-core (DMMA, mma.sync ... f64) tiles fed by TMA.
+//   - CTA tile 128 x 128 x 16, eight consumer warps (2 x 4, each 64 x 32) and one
+//     producer warp group (registers re-split with setmaxnreg); a ring of 32 KB stages filled by cp.async.bulk.tensor and
+//     handed over through full/empty mbarriers.
+//   - Operands land in shared memory in the 128-byte swizzle.  With the k index
+//     of a 16-deep slab permuted (the same permutation for A and B, so the sum is
+//     unchanged) every fragment load is free of bank conflicts: a thread reads
+//     16-byte chunk c = {0,3,5,6}[t] (first half of the slab) or c^1 (second
+//     half), i.e. k = 2c and 2c+1, for all three operand layouts:
+//        k-contiguous tile  [row][16 k]      : one 16-byte load per fragment pair
+//        mn-contiguous tile [16-col group][k][16 cols] : 8-byte loads
+//   - The accumulators stay in registers (FP64 MMA has no TMEM form); the
+//     epilogue adds the bias, applies ReLU or the ReLU mask, and stores or
+//     accumulates 16 bytes per thread per row.
+//   - When the output has too few tiles to fill 148 SMs (weight gradients: the
+//     contraction runs over the batch), the contraction is split across
+//     gridDim.z and a second kernel folds the partial tiles in index order, so
+//     the result is still reproducible.
+// Fallback kernel: a plain shared-memory tiled FMA kernel with full bounds
+// checks for shapes the TMA path cannot take (odd row lengths, unaligned
+// bases) and for tiny problems.
+#include "common.cuh"
+#include "tma.cuh"
+
+#include <cstdlib>
+
+namespace mg {
+
+constexpr int BM = 128, BN = 128, BK = 16;
+constexpr int kStages = 6;
+constexpr int kConsumerWarps = 8;
+constexpr int kProducerWarps = 4;  // one warp group; only its first lane issues copies
+constexpr int kGemmThreads = (kConsumerWarps + kProducerWarps) * 32;  // 384
+// Register split between the warp groups (setmaxnreg): 8*32*232 + 4*32*40 <= 64 K.
+constexpr int kConsumerRegs = 232, kProducerRegs = 40;
+constexpr int kTileBytes = BM * BK * 8;       // 16 KB; A and B tiles are the same size
+constexpr int kStageBytes = 2 * kTileBytes;   // 32 KB
+constexpr int kGemmSmemBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 2 * kStages * 8;
+
+struct GemmEpilogue {
+  double *D;            // output [M][N]
+  const double *aux;    // bias[N] or mask source [M][N]
+  double *partial;      // split-K scratch [splits][M*N], or null
+  int mode;             // MG_EPI_*
+  int accumulate;       // D += instead of D =
+};
+
+__device__ __forceinline__ double2 apply_epilogue(double2 v, const GemmEpilogue &ep, size_t at,
+                                                  int col) {
+  if (ep.mode == MG_EPI_BIAS || ep.mode == MG_EPI_BIAS_RELU) {
+    v.x += __ldg(ep.aux + col);
+    v.y += __ldg(ep.aux + col + 1);
+    if (ep.mode == MG_EPI_BIAS_RELU) {
+      v.x = v.x > 0 ? v.x : 0.0;
+      v.y = v.y > 0 ? v.y : 0.0;
+    }
+  } else if (ep.mode == MG_EPI_RELU_MASK) {
+    const double2 m = *reinterpret_cast<const double2 *>(ep.aux + at);
+    v.x = v.x * (m.x > 0 ? 1.0 : 0.0);
+    v.y = v.y * (m.y > 0 ? 1.0 : 0.0);
+  }
+  if (ep.accumulate) {
+    const double2 old = *reinterpret_cast<const double2 *>(ep.D + at);
+    v.x = old.x + v.x;
+    v.y = old.y + v.y;
+  }
+  return v;
+}
+
+// SHAPE: 0 m8n8k4, 1 m16n8k4, 2 m16n8k8, 3 m16n8k16.
+template <bool A_KCONTIG, bool B_KCONTIG, int SHAPE>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                 GemmEpilogue ep, int M, int N, int K, int tiles_n, int kt_per_split,
+                 int *status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ int abort_flag_s;
+  volatile int *abort_flag = &abort_flag_s;
+
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                              ~static_cast<uintptr_t>(1023));
+  uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + kStages * kStageBytes);
+  uint64_t *empty_bar = full_bar + kStages;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_m = blockIdx.x / tiles_n, tile_n = blockIdx.x % tiles_n;
+  const int m0 = tile_m * BM, n0 = tile_n * BN;
+  const int KT = (K + BK - 1) / BK;
+  const int kt_begin = blockIdx.z * kt_per_split;
+  const int kt_end = min(KT, kt_begin + kt_per_split);
+  const int nkt = kt_end - kt_begin;
+
+  if (threadIdx.x == 0) {
+    abort_flag_s = 0;
+    for (int s = 0; s < kStages; s++) {
+      mbar_init(smem_u32(full_bar + s), 1);
+      mbar_init(smem_u32(empty_bar + s), kConsumerWarps);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (warp >= kConsumerWarps) {
+    // ---------------- producer warp group: one lane drives the TMA ring ----------------
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kProducerRegs));
+    if (warp == kConsumerWarps && lane == 0) {
+      prefetch_tensormap(&mapA);
+      prefetch_tensormap(&mapB);
+      for (int it = 0; it < nkt; ++it) {
+        const int s = it % kStages;
+        if (it >= kStages) {
+          if (!mbar_wait_bounded(smem_u32(empty_bar + s), ((it / kStages) - 1) & 1, abort_flag))
+            break;
+        }
+        const uint32_t bar = smem_u32(full_bar + s);
+        mbar_arrive_expect_tx(bar, kStageBytes);
+        const int k0 = (kt_begin + it) * BK;
+        const uint32_t a_dst = smem_u32(smem + s * kStageBytes);
+        const uint32_t b_dst = a_dst + kTileBytes;
+        if (A_KCONTIG) {
+          tma_load_2d(a_dst, &mapA, k0, m0, bar);
+        } else {
+#pragma unroll
+          for (int b = 0; b < BM / 16; b++) tma_load_2d(a_dst + b * 2048, &mapA, m0 + 16 * b, k0, bar);
+        }
+        if (B_KCONTIG) {
+          tma_load_2d(b_dst, &mapB, k0, n0, bar);
+        } else {
+#pragma unroll
+          for (int b = 0; b < BN / 16; b++) tma_load_2d(b_dst + b * 2048, &mapB, n0 + 16 * b, k0, bar);
+        }
+      }
+    }
+  } else {
+    // ---------------- consumer warp groups ----------------
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kConsumerRegs));
+    const int g = lane >> 2, t = lane & 3;
+    const int wm = (warp >> 2) * 64, wn = (warp & 3) * 32;
+    // 16-byte chunk owned by this thread in the first half-slab; the second
+    // half-slab uses chunk ^ 1.
+    const int c0 = (t << 1) | (__popc(t) & 1);
+
+    double acc[4][4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++)
+#pragma unroll
+        for (int r = 0; r < 4; r++) acc[i][j][r] = 0.0;
+
+    // Loads the fragment pair (k = 2c, 2c+1) for the rows/cols this thread owns.
+    auto load_a = [&](const uint8_t *As, int slab, double2 (&lo)[4], double2 (&hi)[4]) {
+      const int c = c0 ^ slab;
+      if (A_KCONTIG) {
+#pragma unroll
+        for (int mt = 0; mt < 4; mt++) {
+          const int off = (wm + mt * 16 + g) * 128 + ((c ^ g) << 4);
+          lo[mt] = *reinterpret_cast<const double2 *>(As + off);
+          hi[mt] = *reinterpret_cast<const double2 *>(As + off + 8 * 128);
+        }
+      } else {
+        const int ka = 2 * c, kb = 2 * c + 1;
+#pragma unroll
+        for (int mt = 0; mt < 4; mt++) {
+          const int base = ((wm >> 4) + mt) * 2048;
+          const int mlo = g, mhi = g + 8;
+          lo[mt].x = *reinterpret_cast<const double *>(
+              As + base + ka * 128 + ((((mlo >> 1) ^ (ka & 7))) << 4) + (mlo & 1) * 8);
+          lo[mt].y = *reinterpret_cast<const double *>(
+              As + base + kb * 128 + ((((mlo >> 1) ^ (kb & 7))) << 4) + (mlo & 1) * 8);
+          hi[mt].x = *reinterpret_cast<const double *>(
+              As + base + ka * 128 + ((((mhi >> 1) ^ (ka & 7))) << 4) + (mhi & 1) * 8);
+          hi[mt].y = *reinterpret_cast<const double *>(
+              As + base + kb * 128 + ((((mhi >> 1) ^ (kb & 7))) << 4) + (mhi & 1) * 8);
+        }
+      }
+    };
+    auto load_b = [&](const uint8_t *Bs, int slab, double2 (&b)[4]) {
+      const int c = c0 ^ slab;
+      if (B_KCONTIG) {
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+          const int off = (wn + nt * 8 + g) * 128 + ((c ^ g) << 4);
+          b[nt] = *reinterpret_cast<const double2 *>(Bs + off);
+        }
+      } else {
+        const int ka = 2 * c, kb = 2 * c + 1;
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+          const int nl = wn + nt * 8 + g;
+          const int base = (nl >> 4) * 2048, nn = nl & 15;
+          b[nt].x = *reinterpret_cast<const double *>(
+              Bs + base + ka * 128 + ((((nn >> 1) ^ (ka & 7))) << 4) + (nn & 1) * 8);
+          b[nt].y = *reinterpret_cast<const double *>(
+              Bs + base + kb * 128 + ((((nn >> 1) ^ (kb & 7))) << 4) + (nn & 1) * 8);
+        }
+      }
+    };
+
+    bool ok = true;
+    for (int it = 0; it < nkt; ++it) {
+      const int s = it % kStages;
+      if (!mbar_wait_bounded(smem_u32(full_bar + s), (it / kStages) & 1, abort_flag)) {
+        ok = false;
+        break;
+      }
+      const uint8_t *As = smem + s * kStageBytes;
+      const uint8_t *Bs = As + kTileBytes;
+      if (SHAPE == 3) {
+        double2 lo0[4], hi0[4], b0[4], lo1[4], hi1[4], b1[4];
+        load_a(As, 0, lo0, hi0);
+        load_b(Bs, 0, b0);
+        load_a(As, 1, lo1, hi1);
+        load_b(Bs, 1, b1);
+#pragma unroll
+        for (int mt = 0; mt < 4; mt++)
+#pragma unroll
+          for (int nt = 0; nt < 4; nt++)
+            dmma_m16n8k16(acc[mt][nt], lo0[mt].x, hi0[mt].x, lo0[mt].y, hi0[mt].y, lo1[mt].x,
+                          hi1[mt].x, lo1[mt].y, hi1[mt].y, b0[nt].x, b0[nt].y, b1[nt].x, b1[nt].y);
+      } else {
+#pragma unroll
+        for (int slab = 0; slab < 2; slab++) {
+          double2 lo[4], hi[4], b[4];
+          load_a(As, slab, lo, hi);
+          load_b(Bs, slab, b);
+#pragma unroll
+          for (int mt = 0; mt < 4; mt++)
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) {
+              if (SHAPE == 2) {
+                dmma_m16n8k8(acc[mt][nt], lo[mt].x, hi[mt].x, lo[mt].y, hi[mt].y, b[nt].x, b[nt].y);
+              } else if (SHAPE == 1) {
+                dmma_m16n8k4(acc[mt][nt], lo[mt].x, hi[mt].x, b[nt].x);
+                dmma_m16n8k4(acc[mt][nt], lo[mt].y, hi[mt].y, b[nt].y);
+              } else {
+                dmma_m8n8k4(acc[mt][nt][0], acc[mt][nt][1], lo[mt].x, b[nt].x);
+                dmma_m8n8k4(acc[mt][nt][2], acc[mt][nt][3], hi[mt].x, b[nt].x);
+                dmma_m8n8k4(acc[mt][nt][0], acc[mt][nt][1], lo[mt].y, b[nt].y);
+                dmma_m8n8k4(acc[mt][nt][2], acc[mt][nt][3], hi[mt].y, b[nt].y);
+              }
+            }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(empty_bar + s));
+    }
+
+    if (ok) {
+      // ---------------- epilogue ----------------
+      double *dst = ep.partial ? ep.partial + (size_t)blockIdx.z * (size_t)M * (size_t)N : ep.D;
+#pragma unroll
+      for (int mt = 0; mt < 4; mt++) {
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+          const int row = m0 + wm + mt * 16 + g + 8 * h;
+          if (row >= M) continue;
+#pragma unroll
+          for (int nt = 0; nt < 4; nt++) {
+            const int col = n0 + wn + nt * 8 + 2 * t;
+            if (col >= N) continue;
+            const size_t at = (size_t)row * (size_t)N + (size_t)col;
+            double2 v = make_double2(acc[mt][nt][2 * h], acc[mt][nt][2 * h + 1]);
+            if (!ep.partial) v = apply_epilogue(v, ep, at, col);
+            *reinterpret_cast<double2 *>(dst + at) = v;
+          }
+        }
+      }
+    }
+  }
+
+  // A bounded wait gave up somewhere in this CTA: raise the fault word, give the
+  // copies still in flight time to land in this CTA's shared memory, then leave.
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicExch(status, 201);
+    const long long start = clock64();
+    while (clock64() - start < 2000000ll) {
+    }
+  }
+}
+
+// Folds split-K partial tiles in index order and applies the epilogue.
+__global__ void __launch_bounds__(256)
+splitk_finish_kernel(const double *__restrict__ partial, int splits, size_t MN, int N,
+                     GemmEpilogue ep) {
+  const size_t nvec = MN >> 1;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    double2 v = make_double2(0.0, 0.0);
+    for (int s = 0; s < splits; s++) {
+      const double2 p = __ldcs(reinterpret_cast<const double2 *>(partial + (size_t)s * MN) + i);
+      v.x += p.x;
+      v.y += p.y;
+    }
+    const size_t at = i * 2;
+    v = apply_epilogue(v, ep, at, (int)(at % (size_t)N));
+    *reinterpret_cast<double2 *>(ep.D + at) = v;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Fallback: D[m,n] (+)= sum_k A(m,k) B(k,n) with arbitrary element strides.
+// 64 x 64 x 16 tiles, 256 threads, 4 x 4 outputs per thread, full bounds checks.
+// ---------------------------------------------------------------------------
+struct StridedOperands {
+  const double *A;
+  const double *B;
+  long long sAm, sAk, sBk, sBn;
+};
+
+__global__ void __launch_bounds__(256)
+gemm_fallback_kernel(StridedOperands op, GemmEpilogue ep, int M, int N, int K) {
+  constexpr int TM = 64, TN = 64, TK = 16;
+  __shared__ double As[TK][TM + 1];
+  __shared__ double Bs[TK][TN + 1];
+  const int tid = threadIdx.x;
+  const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
+  const int ty = tid / 16, tx = tid % 16;  // thread owns rows ty*4.., cols tx*4..
+  double acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[i][j] = 0.0;
+
+  const bool a_k_fast = (op.sAk == 1);
+  const bool b_n_fast = (op.sBn == 1);
+  for (int k0 = 0; k0 < K; k0 += TK) {
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      const int idx = tid + e * 256;  // 0..1023
+      int m, k;
+      if (a_k_fast) { m = idx / TK; k = idx % TK; } else { m = idx % TM; k = idx / TM; }
+      const int gm = m0 + m, gk = k0 + k;
+      As[k][m] = (gm < M && gk < K) ? op.A[(long long)gm * op.sAm + (long long)gk * op.sAk] : 0.0;
+      int n, kk;
+      if (b_n_fast) { n = idx % TN; kk = idx / TN; } else { n = idx / TK; kk = idx % TK; }
+      const int gn = n0 + n, gk2 = k0 + kk;
+      Bs[kk][n] = (gn < N && gk2 < K) ? op.B[(long long)gk2 * op.sBk + (long long)gn * op.sBn] : 0.0;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < TK; k++) {
+      double a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; j++) b[j] = Bs[k][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = fma(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int row = m0 + ty * 4 + i;
+    if (row >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int col = n0 + tx * 4 + j;
+      if (col >= N) continue;
+      const size_t at = (size_t)row * (size_t)N + (size_t)col;
+      double v = acc[i][j];
+      if (ep.mode == MG_EPI_BIAS || ep.mode == MG_EPI_BIAS_RELU) {
+        v += ep.aux[col];
+        if (ep.mode == MG_EPI_BIAS_RELU) v = v > 0 ? v : 0.0;
+      } else if (ep.mode == MG_EPI_RELU_MASK) {
+        v = v * (ep.aux[at] > 0 ? 1.0 : 0.0);
+      }
+      if (ep.accumulate) v = ep.D[at] + v;
+      ep.D[at] = v;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host dispatch
+// ---------------------------------------------------------------------------
+struct GemmDesc {
+  const double *A;  // a_kcontig ? [M][K] : [K][M]
+  const double *B;  // b_kcontig ? [N][K] : [K][N]
+  double *D;        // [M][N]
+  size_t M, N, K;
+  bool a_kcontig, b_kcontig;
+  int accumulate, mode;
+  const double *aux;
+};
+
+static int g_gemm_path = 0;    // 0 auto, 1 fallback only, 2 tensor-core whenever eligible
+static int g_dmma_shape = -1;  // -1: default
+
+static int default_dmma_shape() {
+  const char *v = std::getenv("MG_DMMA_SHAPE");
+  if (v && *v) {
+    int s = std::atoi(v);
+    if (s >= 0 && s <= 3) return s;
+  }
+  return 2;
+}
+
+template <bool AK, bool BK_, int SHAPE>
+static int launch_dmma(const CUtensorMap &ma, const CUtensorMap &mb, const GemmEpilogue &ep, int M,
+                       int N, int K, int tiles_m, int tiles_n, int splits, int kt_per_split) {
+  static bool configured = false;
+  auto kernel = dmma_gemm_kernel<AK, BK_, SHAPE>;
+  if (!configured) {
+    MG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kGemmSmemBytes));
+    configured = true;
+  }
+  Context &c = ctx();
+  dim3 grid((unsigned)(tiles_m * tiles_n), 1, (unsigned)splits);
+  kernel<<<grid, kGemmThreads, kGemmSmemBytes, c.stream>>>(ma, mb, ep, M, N, K, tiles_n,
+                                                            kt_per_split, c.kernel_status);
+  MG_LAUNCH_CHECK("dmma_gemm");
+  return MG_OK;
+}
+
+template <bool AK, bool BK_>
+static int launch_dmma_shape(int shape, const CUtensorMap &ma, const CUtensorMap &mb,
+                             const GemmEpilogue &ep, int M, int N, int K, int tiles_m, int tiles_n,
+                             int splits, int kt_per_split) {
+  switch (shape) {
+    case 0: return launch_dmma<AK, BK_, 0>(ma, mb, ep, M, N, K, tiles_m, tiles_n, splits, kt_per_split);
+    case 1: return launch_dmma<AK, BK_, 1>(ma, mb, ep, M, N, K, tiles_m, tiles_n, splits, kt_per_split);
+    case 3: return launch_dmma<AK, BK_, 3>(ma, mb, ep, M, N, K, tiles_m, tiles_n, splits, kt_per_split);
+    default: return launch_dmma<AK, BK_, 2>(ma, mb, ep, M, N, K, tiles_m, tiles_n, splits, kt_per_split);
+  }
+}
+
+// Number of contraction splits: the smallest count that fills at least 95% of
+// the last wave of CTAs on the device, with at least 16 k-tiles per split.
+static int choose_splits(int tiles, int KT, int sms) {
+  if (tiles >= 4 * sms) return 1;
+  int max_s = KT / 16;
+  if (max_s > 64) max_s = 64;
+  if (max_s < 1) max_s = 1;
+  int best = 1;
+  double best_eff = 0.0;
+  for (int s = 1; s <= max_s; s++) {
+    const int ctas = tiles * s;
+    const int waves = (ctas + sms - 1) / sms;
+    const double eff = (double)ctas / ((double)waves * sms);
+    if (eff > best_eff + 1e-9) {
+      best_eff = eff;
+      best = s;
+    }
+    if (eff >= 0.95) return s;
+  }
+  return best;
+}
+
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+static bool dmma_eligible(const GemmDesc &d) {
+  const size_t a_row = d.a_kcontig ? d.K : d.M;
+  const size_t b_row = d.b_kcontig ? d.K : d.N;
+  if ((a_row | b_row | d.N) & 1) return false;
+  if (!aligned16(d.A) || !aligned16(d.B) || !aligned16(d.D)) return false;
+  if (d.mode == MG_EPI_RELU_MASK && !aligned16(d.aux)) return false;
+  const size_t lim = (size_t)1 << 30;
+  if (d.M >= lim || d.N >= lim || d.K >= lim) return false;
+  return true;
+}
+
+static int run_gemm(const GemmDesc &d) {
+  if (d.M == 0 || d.N == 0) return MG_OK;
+  Context &c = ctx();
+  GemmEpilogue ep;
+  ep.D = d.D;
+  ep.aux = d.aux;
+  ep.partial = nullptr;
+  ep.mode = d.mode;
+  ep.accumulate = d.accumulate;
+  if ((d.mode == MG_EPI_BIAS || d.mode == MG_EPI_BIAS_RELU || d.mode == MG_EPI_RELU_MASK) && !d.aux)
+    return fail(MG_ERR_INVALID, "gemm: epilogue %d needs its auxiliary operand", d.mode);
+  if (d.K == 0) {
+    // Empty contraction: the product is all zeros; only the epilogue remains.
+    if (d.accumulate && d.mode == MG_EPI_NONE) return MG_OK;
+    if (d.accumulate && d.mode == MG_EPI_RELU_MASK) return MG_OK;
+  }
+
+  bool use_dmma = dmma_eligible(d) && d.K > 0;
+  if (g_gemm_path == 1) use_dmma = false;
+  if (g_gemm_path == 0 && use_dmma && d.M * d.N * d.K < (size_t)64 * 64 * 64) use_dmma = false;
+
+  const int M = (int)d.M, N = (int)d.N, K = (int)d.K;
+  if (!use_dmma) {
+    if (d.M >= ((size_t)1 << 31) || d.N >= ((size_t)1 << 31) || d.K >= ((size_t)1 << 31))
+      return fail(MG_ERR_INVALID, "gemm: dimension too large");
+    StridedOperands op;
+    op.A = d.A;
+    op.B = d.B;
+    if (d.a_kcontig) { op.sAm = (long long)d.K; op.sAk = 1; } else { op.sAm = 1; op.sAk = (long long)d.M; }
+    if (d.b_kcontig) { op.sBk = 1; op.sBn = (long long)d.K; } else { op.sBk = (long long)d.N; op.sBn = 1; }
+    dim3 grid((unsigned)((N + 63) / 64), (unsigned)((M + 63) / 64));
+    if (grid.y > 65535) return fail(MG_ERR_INVALID, "gemm fallback: too many row tiles (%u)", grid.y);
+    gemm_fallback_kernel<<<grid, 256, 0, c.stream>>>(op, ep, M, N, K);
+    MG_LAUNCH_CHECK("gemm_fallback");
+    return MG_OK;
+  }
+
+  CUtensorMap ma, mb;
+  bool ok_a = d.a_kcontig ? make_tensor_map_f64(&ma, d.A, d.M, d.K, BK, BM)
+                          : make_tensor_map_f64(&ma, d.A, d.K, d.M, 16, BK);
+  bool ok_b = d.b_kcontig ? make_tensor_map_f64(&mb, d.B, d.N, d.K, BK, BN)
+                          : make_tensor_map_f64(&mb, d.B, d.K, d.N, 16, BK);
+  if (!ok_a || !ok_b) return fail(MG_ERR_CUDA, "gemm: cuTensorMapEncodeTiled failed");
+
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int KT = (K + BK - 1) / BK;
+  int splits = choose_splits(tiles_m * tiles_n, KT, c.sm_count);
+  int kt_per_split = (KT + splits - 1) / splits;
+  splits = (KT + kt_per_split - 1) / kt_per_split;
+  if (splits > 1) {
+    int rc = ensure_scratch(&c.splitk_scratch, &c.splitk_scratch_elems,
+                            (size_t)splits * d.M * d.N);
+    if (rc != MG_OK) return rc;
+    ep.partial = c.splitk_scratch;
+  }
+  const int shape = g_dmma_shape >= 0 ? g_dmma_shape : default_dmma_shape();
+  int rc;
+  if (d.a_kcontig && !d.b_kcontig)
+    rc = launch_dmma_shape<true, false>(shape, ma, mb, ep, M, N, K, tiles_m, tiles_n, splits, kt_per_split);
+  else if (d.a_kcontig && d.b_kcontig)
+    rc = launch_dmma_shape<true, true>(shape, ma, mb, ep, M, N, K, tiles_m, tiles_n, splits, kt_per_split);
+  else if (!d.a_kcontig && !d.b_kcontig)
+    rc = launch_dmma_shape<false, false>(shape, ma, mb, ep, M, N, K, tiles_m, tiles_n, splits, kt_per_split);
+  else
+    return fail(MG_ERR_INVALID, "gemm: unsupported operand layout");
+  if (rc != MG_OK) return rc;
+  if (splits > 1) {
+    GemmEpilogue fin = ep;
+    fin.partial = nullptr;
+    const size_t MN = d.M * d.N;
+    splitk_finish_kernel<<<grid_for(MN / 2, 256, 8), 256, 0, c.stream>>>(c.splitk_scratch, splits,
+                                                                         MN, N, fin);
+    MG_LAUNCH_CHECK("splitk_finish");
+  }
+  return MG_OK;
+}
+
+}  // namespace mg
+
+using namespace mg;
+
+extern "C" {
+
+int mg_gemm_config(int path, int dmma_shape) {
+  if (path < 0 || path > 2) return fail(MG_ERR_INVALID, "mg_gemm_config: path must be 0, 1 or 2");
+  if (dmma_shape < -1 || dmma_shape > 3)
+    return fail(MG_ERR_INVALID, "mg_gemm_config: shape must be -1..3");
+  g_gemm_path = path;
+  g_dmma_shape = dmma_shape;
+  return MG_OK;
+}
+
+int mg_gemm_nn(const double *A, const double *B, double *C, size_t M, size_t N, size_t K,
+               int accumulate, int epilogue, const double *bias) {
+  MG_ENSURE_INIT();
+  if (M && N && (!C || (K && (!A || !B)))) return fail(MG_ERR_INVALID, "mg_gemm_nn: null pointer");
+  if (epilogue != MG_EPI_NONE && epilogue != MG_EPI_BIAS && epilogue != MG_EPI_BIAS_RELU)
+    return fail(MG_ERR_INVALID, "mg_gemm_nn: epilogue %d not valid here", epilogue);
+  GemmDesc d{A, B, C, M, N, K, true, false, accumulate, epilogue, bias};
+  return run_gemm(d);
+}
+
+int mg_gemm_nt(const double *G, const double *B, double *dA, size_t M, size_t N, size_t K,
+               int accumulate, int epilogue, const double *mask_src) {
+  MG_ENSURE_INIT();
+  if (M && K && (!dA || (N && (!G || !B)))) return fail(MG_ERR_INVALID, "mg_gemm_nt: null pointer");
+  if (epilogue != MG_EPI_NONE && epilogue != MG_EPI_RELU_MASK)
+    return fail(MG_ERR_INVALID, "mg_gemm_nt: epilogue %d not valid here", epilogue);
+  // Output [M][K]; contraction over N; G is [M][N] (k-contiguous), B is [K][N]
+  // (output-column major, k-contiguous).
+  GemmDesc d{G, B, dA, M, K, N, true, true, accumulate, epilogue, mask_src};
+  return run_gemm(d);
+}
+
+int mg_gemm_tn(const double *A, const double *G, double *dB, size_t M, size_t N, size_t K,
+               int accumulate) {
+  MG_ENSURE_INIT();
+  if (K && N && (!dB || (M && (!A || !G)))) return fail(MG_ERR_INVALID, "mg_gemm_tn: null pointer");
+  // Output [K][N]; contraction over M; A is [M][K] (output-row contiguous),
+  // G is [M][N] (output-column contiguous).
+  GemmDesc d{A, G, dB, K, N, M, false, false, accumulate, MG_EPI_NONE, nullptr};
+  return run_gemm(d);
+}
+
+}  // extern "C"

@@ -1,0 +1,431 @@
+// Reductions: full sum, last-axis sum, column sum (bias gradients), softmax
+// cross-entropy and row argmax.
+//
+// Every reduction has a fixed association order: per-thread strided partial
+// sums, a warp-shuffle butterfly, a shared-memory tree across the warps of a
+// CTA, and a second level over a fixed number of per-CTA partials that the last
+// CTA to finish folds in index order.  The order depends only on the problem
+// size, never on scheduling, so a result is reproducible from run to run.
+#include "common.cuh"
+
+namespace mg {
+
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  return v;
+}
+
+__device__ __forceinline__ double warp_max(double v) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v = fmax(v, __shfl_xor_sync(0xffffffffu, v, off));
+  return v;
+}
+
+// Sum of `v` over the CTA (blockDim.x a multiple of 32, at most 1024); the
+// result is valid in thread 0.
+__device__ __forceinline__ double block_sum(double v, double *smem32) {
+  const int lane_id = threadIdx.x & 31, warp_id = threadIdx.x >> 5;
+  v = warp_sum(v);
+  if (lane_id == 0) smem32[warp_id] = v;
+  __syncthreads();
+  const int nwarps = (blockDim.x + 31) >> 5;
+  double t = (threadIdx.x < nwarps) ? smem32[threadIdx.x] : 0.0;
+  if (warp_id == 0) t = warp_sum(t);
+  __syncthreads();
+  return t;
+}
+
+// Second level: CTA `blockIdx.x` publishes its partial; the last CTA to arrive
+// (ticket counter) sums all partials in index order, scales, and stores or
+// accumulates the result.  The ticket is reset for the next launch.
+__device__ __forceinline__ void finish_partials(double partial, double *partials,
+                                                unsigned int *ticket, double *out, double scale,
+                                                double *smem32) {
+  __shared__ bool is_last;
+  if (threadIdx.x == 0) {
+    partials[blockIdx.x] = partial;
+    __threadfence();
+    unsigned int t = atomicAdd(ticket, 1u);
+    is_last = (t == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  double acc = 0.0;
+  for (unsigned i = threadIdx.x; i < gridDim.x; i += blockDim.x) acc += __ldcg(partials + i);
+  acc = block_sum(acc, smem32);
+  if (threadIdx.x == 0) {
+    out[0] = acc * scale;
+    *ticket = 0u;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Full sum (src/ops/Reduction.cpp:17-21).  8 B of traffic per element.
+// ---------------------------------------------------------------------------
+template <int VEC>
+__global__ void __launch_bounds__(kReduceThreads)
+sum_all_kernel(const double *__restrict__ x, size_t n, double *partials, unsigned int *ticket,
+               double *out) {
+  __shared__ double smem32[32];
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
+  if (VEC == 2) {
+    const double2 *xv = reinterpret_cast<const double2 *>(x);
+    const size_t nvec = n >> 1;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+      double2 v0 = __ldcs(xv + i), v1 = __ldcs(xv + i + stride), v2 = __ldcs(xv + i + 2 * stride),
+              v3 = __ldcs(xv + i + 3 * stride);
+      a0 += v0.x + v0.y;
+      a1 += v1.x + v1.y;
+      a2 += v2.x + v2.y;
+      a3 += v3.x + v3.y;
+    }
+    for (; i < nvec; i += stride) {
+      double2 v = __ldcs(xv + i);
+      a0 += v.x + v.y;
+    }
+    if ((n & 1) && blockIdx.x == 0 && threadIdx.x == 0) a1 += x[n - 1];
+  } else {
+    for (; i < n; i += stride) a0 += __ldcs(x + i);
+  }
+  double t = block_sum((a0 + a1) + (a2 + a3), smem32);
+  finish_partials(t, partials, ticket, out, 1.0, smem32);
+}
+
+// ---------------------------------------------------------------------------
+// Last-axis sum [M,N] -> [M]: one warp per row, lanes stride the row in 16-byte
+// words, butterfly at the end.
+// ---------------------------------------------------------------------------
+template <int VEC>
+__global__ void __launch_bounds__(256)
+sum_lastaxis_kernel(const double *__restrict__ x, double *__restrict__ out, size_t M, size_t N) {
+  const int lane_id = threadIdx.x & 31;
+  const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  size_t row = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  for (; row < M; row += warps) {
+    const double *r = x + row * N;
+    double a0 = 0.0, a1 = 0.0;
+    if (VEC == 2) {
+      const double2 *rv = reinterpret_cast<const double2 *>(r);
+      const size_t nvec = N >> 1;
+      size_t j = lane_id;
+      for (; j + 32 < nvec; j += 64) {
+        double2 v0 = __ldcs(rv + j), v1 = __ldcs(rv + j + 32);
+        a0 += v0.x + v0.y;
+        a1 += v1.x + v1.y;
+      }
+      for (; j < nvec; j += 32) {
+        double2 v = __ldcs(rv + j);
+        a0 += v.x + v.y;
+      }
+    } else {
+      for (size_t j = lane_id; j < N; j += 32) a0 += __ldcs(r + j);
+    }
+    double t = warp_sum(a0 + a1);
+    if (lane_id == 0) out[row] = t;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Column sum over rows (bias gradient; add_row backward), optionally fused with
+// the pass-through gx += g so that g is read once: 24 B per element with gx,
+// 8 B without.
+//   stage 1: grid (column tiles, S row chunks); thread (tx, ty) walks rows
+//            ty, ty+TY, ... of its chunk for column word tx; shared-memory fold
+//            over ty in index order -> partials[s][col]
+//   stage 2: one thread per column folds the S partials in index order.
+// ---------------------------------------------------------------------------
+template <int VEC, int TX>
+__global__ void __launch_bounds__(256)
+colsum_partial_kernel(const double *__restrict__ g, double *__restrict__ gx, bool gx_accumulate,
+                      double *__restrict__ partials, size_t M, size_t N, size_t rows_per_chunk) {
+  constexpr int TY = 256 / TX;
+  __shared__ double sm[TY][TX * VEC + 1];
+  const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
+  const size_t ncol = N / VEC;
+  const size_t cv = (size_t)blockIdx.x * TX + tx;
+  const size_t r0 = (size_t)blockIdx.y * rows_per_chunk;
+  size_t r1 = r0 + rows_per_chunk;
+  if (r1 > M) r1 = M;
+  double acc[VEC];
+#pragma unroll
+  for (int l = 0; l < VEC; l++) acc[l] = 0.0;
+  if (cv < ncol) {
+    for (size_t r = r0 + ty; r < r1; r += TY) {
+      const size_t at = r * ncol + cv;
+      if (VEC == 2) {
+        double2 v = __ldcs(reinterpret_cast<const double2 *>(g) + at);
+        acc[0] += v.x;
+        acc[VEC - 1] += v.y;
+        if (gx) {
+          double2 *p = reinterpret_cast<double2 *>(gx) + at;
+          double2 o = gx_accumulate ? __ldcs(p) : make_double2(0.0, 0.0);
+          o.x += v.x;
+          o.y += v.y;
+          __stcs(p, o);
+        }
+      } else {
+        double v = __ldcs(g + at);
+        acc[0] += v;
+        if (gx) {
+          double o = gx_accumulate ? __ldcs(gx + at) : 0.0;
+          __stcs(gx + at, o + v);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int l = 0; l < VEC; l++) sm[ty][tx * VEC + l] = acc[l];
+  __syncthreads();
+  if (ty == 0 && cv < ncol) {
+#pragma unroll
+    for (int l = 0; l < VEC; l++) {
+      double t = 0.0;
+      for (int y = 0; y < TY; y++) t += sm[y][tx * VEC + l];
+      partials[(size_t)blockIdx.y * N + cv * VEC + l] = t;
+    }
+  }
+}
+
+__global__ void colsum_finish_kernel(const double *__restrict__ partials, size_t S, size_t N,
+                                     double *__restrict__ out, bool accumulate) {
+  const size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= N) return;
+  double t = accumulate ? out[j] : 0.0;
+  for (size_t s = 0; s < S; s++) t += partials[s * N + j];
+  out[j] = t;
+}
+
+// ---------------------------------------------------------------------------
+// Softmax cross-entropy over rows, one warp per row.
+//   m = max_j z_j ; s = sum_j exp(z_j - m) ; loss_i = -(z_y - m - log s)
+// Forward folds the per-row losses with the same two-level scheme as the full
+// sum and divides by `denom`.  Backward recomputes m and s (the logits row is
+// C doubles, far cheaper to re-read than to save the probabilities).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void row_max_sumexp(const double *r, size_t C, int lane_id, double &mx,
+                                               double &s) {
+  double m = -INFINITY;
+  for (size_t j = lane_id; j < C; j += 32) m = fmax(m, r[j]);
+  m = warp_max(m);
+  double t = 0.0;
+  for (size_t j = lane_id; j < C; j += 32) t += exp(r[j] - m);
+  s = warp_sum(t);
+  mx = m;
+}
+
+__global__ void __launch_bounds__(kReduceThreads)
+softmax_xent_fwd_kernel(const double *__restrict__ z, const int *__restrict__ labels, size_t M,
+                        size_t C, double inv_scale_denom, double *partials, unsigned int *ticket,
+                        double *out, int *status) {
+  __shared__ double smem32[32];
+  const int lane_id = threadIdx.x & 31;
+  const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  double local = 0.0;
+  for (size_t row = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < M; row += warps) {
+    const double *r = z + row * C;
+    double mx, s;
+    row_max_sumexp(r, C, lane_id, mx, s);
+    if (lane_id == 0) {
+      int y = labels[row];
+      if (y < 0 || (size_t)y >= C) {
+        atomicExch(status, 101);  // label out of range: flag it, count no loss
+      } else {
+        local += -(r[y] - mx - log(s));
+      }
+    }
+  }
+  double t = block_sum(local, smem32);
+  finish_partials(t, partials, ticket, out, inv_scale_denom, smem32);
+}
+
+__global__ void __launch_bounds__(256)
+softmax_xent_bwd_kernel(const double *__restrict__ z, const int *__restrict__ labels,
+                        const double *__restrict__ gloss, double *__restrict__ gz, size_t M,
+                        size_t C, double denom, bool accumulate) {
+  const int lane_id = threadIdx.x & 31;
+  const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  const double gl = __ldg(gloss);
+  for (size_t row = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < M; row += warps) {
+    const double *r = z + row * C;
+    double mx, s;
+    row_max_sumexp(r, C, lane_id, mx, s);
+    const int y = labels[row];
+    for (size_t j = lane_id; j < C; j += 32) {
+      const double p = exp(r[j] - mx) / s;
+      const double v = gl * (p - ((int)j == y ? 1.0 : 0.0)) / denom;
+      double *dst = gz + row * C + j;
+      *dst = accumulate ? (*dst + v) : v;
+    }
+  }
+}
+
+// Row argmax: first index of the strict maximum (ties keep the lower index).
+__global__ void __launch_bounds__(256)
+argmax_rows_kernel(const double *__restrict__ x, int *__restrict__ out, size_t M, size_t N) {
+  const int lane_id = threadIdx.x & 31;
+  const size_t warps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  for (size_t row = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < M; row += warps) {
+    const double *r = x + row * N;
+    double best = -INFINITY;
+    unsigned long long best_j = ~0ull;  // "no candidate yet"
+    for (size_t j = lane_id; j < N; j += 32) {
+      double v = r[j];
+      if (best_j == ~0ull || v > best) {
+        best = v;
+        best_j = j;
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      double ov = __shfl_xor_sync(0xffffffffu, best, off);
+      unsigned long long oj = __shfl_xor_sync(0xffffffffu, best_j, off);
+      if (oj != ~0ull && (best_j == ~0ull || ov > best || (ov == best && oj < best_j))) {
+        best = ov;
+        best_j = oj;
+      }
+    }
+    if (lane_id == 0) out[row] = (int)best_j;
+  }
+}
+
+static unsigned reduce_grid(size_t work_per_thread_units) {
+  // Enough CTAs that each thread has a few units of work, never more than the
+  // fixed partial count.
+  size_t need = (work_per_thread_units + (size_t)kReduceThreads * 4 - 1) / ((size_t)kReduceThreads * 4);
+  if (need < 1) need = 1;
+  if (need > (size_t)kReducePartials) need = kReducePartials;
+  return (unsigned)need;
+}
+
+}  // namespace mg
+
+using namespace mg;
+
+extern "C" {
+
+int mg_sum_all_fwd(const double *x, double *out1, size_t n) {
+  MG_ENSURE_INIT();
+  if (!out1) return fail(MG_ERR_INVALID, "mg_sum_all_fwd: null output");
+  if (n == 0) return mg_fill(out1, 0.0, 1);
+  if (!x) return fail(MG_ERR_INVALID, "mg_sum_all_fwd: null input");
+  Context &c = ctx();
+  if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    unsigned grid = reduce_grid((n + 1) / 2);
+    sum_all_kernel<2><<<grid, kReduceThreads, 0, c.stream>>>(x, n, c.reduce_partials,
+                                                             c.reduce_ticket, out1);
+  } else {
+    unsigned grid = reduce_grid(n);
+    sum_all_kernel<1><<<grid, kReduceThreads, 0, c.stream>>>(x, n, c.reduce_partials,
+                                                             c.reduce_ticket, out1);
+  }
+  MG_LAUNCH_CHECK("sum_all_fwd");
+  return MG_OK;
+}
+
+int mg_sum_lastaxis_fwd(const double *x, double *out, size_t M, size_t N) {
+  MG_ENSURE_INIT();
+  if (M == 0) return MG_OK;
+  if (!out) return fail(MG_ERR_INVALID, "mg_sum_lastaxis_fwd: null output");
+  if (N == 0) return mg_fill(out, 0.0, M);
+  if (!x) return fail(MG_ERR_INVALID, "mg_sum_lastaxis_fwd: null input");
+  Context &c = ctx();
+  unsigned grid = grid_for(M * 32, 256, 8);
+  if ((N % 2 == 0) && (reinterpret_cast<uintptr_t>(x) & 15) == 0)
+    sum_lastaxis_kernel<2><<<grid, 256, 0, c.stream>>>(x, out, M, N);
+  else
+    sum_lastaxis_kernel<1><<<grid, 256, 0, c.stream>>>(x, out, M, N);
+  MG_LAUNCH_CHECK("sum_lastaxis_fwd");
+  return MG_OK;
+}
+
+int mg_add_row_bwd(const double *g, double *gx, double *grow, size_t M, size_t N, int flags) {
+  MG_ENSURE_INIT();
+  if (M == 0 || N == 0 || (!gx && !grow)) return MG_OK;
+  if (!g) return fail(MG_ERR_INVALID, "mg_add_row_bwd: null upstream gradient");
+  if (!grow) {
+    // Only the pass-through: a plain accumulate.
+    return mg_unary_bwd(MG_SADD, nullptr, nullptr, 0.0, g, gx, M * N, flags & MG_ACC_STORE_A);
+  }
+  Context &c = ctx();
+  uintptr_t bits = reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(gx);
+  const bool vec = (N % 2 == 0) && (bits & 15) == 0;
+  const size_t ncol = vec ? N / 2 : N;
+  const int TX = ncol >= 32 ? 32 : 8;
+  const int TY = 256 / TX;
+  const size_t gridx = (ncol + TX - 1) / TX;
+  // Row chunks: about four waves of CTAs, each CTA at least 4 passes of TY rows.
+  size_t S = (size_t)(148 * 4) / gridx;
+  size_t max_s = (M + (size_t)TY * 4 - 1) / ((size_t)TY * 4);
+  if (S > max_s) S = max_s;
+  if (S < 1) S = 1;
+  if (S > 65535) S = 65535;
+  const size_t rows_per_chunk = (M + S - 1) / S;
+  S = (M + rows_per_chunk - 1) / rows_per_chunk;
+  int rc = ensure_scratch(&c.colsum_scratch, &c.colsum_scratch_elems, S * N);
+  if (rc != MG_OK) return rc;
+  dim3 grid((unsigned)gridx, (unsigned)S);
+  const bool gx_acc = !(flags & MG_ACC_STORE_A);
+  if (vec) {
+    if (TX == 32)
+      colsum_partial_kernel<2, 32><<<grid, 256, 0, c.stream>>>(g, gx, gx_acc, c.colsum_scratch, M, N, rows_per_chunk);
+    else
+      colsum_partial_kernel<2, 8><<<grid, 256, 0, c.stream>>>(g, gx, gx_acc, c.colsum_scratch, M, N, rows_per_chunk);
+  } else {
+    if (TX == 32)
+      colsum_partial_kernel<1, 32><<<grid, 256, 0, c.stream>>>(g, gx, gx_acc, c.colsum_scratch, M, N, rows_per_chunk);
+    else
+      colsum_partial_kernel<1, 8><<<grid, 256, 0, c.stream>>>(g, gx, gx_acc, c.colsum_scratch, M, N, rows_per_chunk);
+  }
+  MG_LAUNCH_CHECK("colsum_partial");
+  colsum_finish_kernel<<<(unsigned)((N + 255) / 256), 256, 0, c.stream>>>(
+      c.colsum_scratch, S, N, grow, !(flags & MG_ACC_STORE_B));
+  MG_LAUNCH_CHECK("colsum_finish");
+  return MG_OK;
+}
+
+int mg_softmax_xent_fwd(const double *logits, const int *labels, double *loss1, size_t M,
+                        size_t C, double denom) {
+  MG_ENSURE_INIT();
+  if (!loss1) return fail(MG_ERR_INVALID, "mg_softmax_xent_fwd: null output");
+  if (M == 0 || C == 0) return mg_fill(loss1, 0.0, 1);
+  if (!logits || !labels) return fail(MG_ERR_INVALID, "mg_softmax_xent_fwd: null input");
+  if (!(denom > 0.0)) return fail(MG_ERR_INVALID, "mg_softmax_xent_fwd: denom must be positive");
+  Context &c = ctx();
+  size_t need = (M * 32 + kReduceThreads - 1) / kReduceThreads;
+  unsigned grid = (unsigned)(need < (size_t)kReducePartials ? (need ? need : 1) : kReducePartials);
+  softmax_xent_fwd_kernel<<<grid, kReduceThreads, 0, c.stream>>>(
+      logits, labels, M, C, 1.0 / denom, c.reduce_partials, c.reduce_ticket, loss1, c.kernel_status);
+  MG_LAUNCH_CHECK("softmax_xent_fwd");
+  return MG_OK;
+}
+
+int mg_softmax_xent_bwd(const double *logits, const int *labels, const double *gloss1,
+                        double *glogits, size_t M, size_t C, double denom, int flags) {
+  MG_ENSURE_INIT();
+  if (M == 0 || C == 0 || !glogits) return MG_OK;
+  if (!logits || !labels || !gloss1) return fail(MG_ERR_INVALID, "mg_softmax_xent_bwd: null input");
+  if (!(denom > 0.0)) return fail(MG_ERR_INVALID, "mg_softmax_xent_bwd: denom must be positive");
+  Context &c = ctx();
+  unsigned grid = grid_for(M * 32, 256, 8);
+  softmax_xent_bwd_kernel<<<grid, 256, 0, c.stream>>>(logits, labels, gloss1, glogits, M, C, denom,
+                                                      !(flags & MG_ACC_STORE_A));
+  MG_LAUNCH_CHECK("softmax_xent_bwd");
+  return MG_OK;
+}
+
+int mg_argmax_rows(const double *x, int *out, size_t M, size_t N) {
+  MG_ENSURE_INIT();
+  if (M == 0) return MG_OK;
+  if (!x || !out) return fail(MG_ERR_INVALID, "mg_argmax_rows: null pointer");
+  if (N == 0) return fail(MG_ERR_INVALID, "mg_argmax_rows: rows are empty");
+  Context &c = ctx();
+  argmax_rows_kernel<<<grid_for(M * 32, 256, 8), 256, 0, c.stream>>>(x, out, M, N);
+  MG_LAUNCH_CHECK("argmax_rows");
+  return MG_OK;
+}
+
+}  // extern "C"

@@ -334,16 +334,25 @@ mgt_tensor mgt_sum_axis(mgt_tensor a, int axis) {
   return guard_tensor([&] { return a->p->sum(axis); });
 }
 
-mgt_tensor mgt_softmax_cross_entropy(mgt_tensor logits, mgt_tensor labels) {
-  return guard_tensor([&] { return softmax_cross_entropy(logits->p, labels->p); });
+mgt_tensor mgt_softmax_cross_entropy(mgt_tensor logits, mgt_tensor labels, double denom) {
+  return guard_tensor([&] { return softmax_cross_entropy(logits->p, labels->p, denom); });
 }
 
-mgt_tensor mgt_softmax_cross_entropy_host(mgt_tensor logits, const int *labels_host,
-                                          size_t nrows) {
+mgt_tensor mgt_softmax_cross_entropy_host(mgt_tensor logits, const int *labels_host, size_t nrows,
+                                          double denom) {
   return guard_tensor([&] {
-    return softmax_cross_entropy(logits->p, std::vector<int>(labels_host, labels_host + nrows));
+    return softmax_cross_entropy(logits->p, std::vector<int>(labels_host, labels_host + nrows),
+                                 denom);
   });
 }
+
+mgt_tensor mgt_new_from_host(const size_t *shape, size_t ndim, const double *values) {
+  return guard_tensor(
+      [&] { return Tensor::from_host(std::vector<size_t>(shape, shape + ndim), values); });
+}
+
+int mgt_comm_rank(void) { return micrograd::comm_rank(); }
+int mgt_comm_world(void) { return micrograd::comm_world(); }
 
 int mgt_argmax_rows(mgt_tensor x, int *out, size_t nrows) {
   return guard_int([&] {

@@ -1,0 +1,189 @@
+// detail::Storage — device buffer + lazily materialised host mirror.
+#include "micrograd/detail/Storage.h"
+
+#include <stdexcept>
+#include <string>
+
+#include "mg_cuda.h"
+
+namespace micrograd::detail {
+
+void check(int rc, const char *what) {
+  if (rc != MG_OK) {
+    throw std::runtime_error(std::string(what) + ": " + mg_last_error());
+  }
+}
+
+Storage::~Storage() {
+  if (dev_ && owns_dev_) {
+    mg_free(dev_);
+  }
+}
+
+void Storage::init_zero(size_t n) {
+  size_ = n;
+  zero_ = true;
+  dev_valid_ = false;
+  host_valid_ = false;
+}
+
+void Storage::ensure_device_buffer() {
+  if (!dev_) {
+    check(mg_alloc(size_, &dev_), "device allocation");
+    owns_dev_ = true;
+  }
+}
+
+void Storage::init_from_host(std::vector<double> &&values) {
+  size_ = values.size();
+  ensure_device_buffer();
+  // A copy from pageable memory has been staged when the call returns, so the
+  // temporary can be released right away; the device copy is the only one kept.
+  check(mg_upload(dev_, values.data(), size_), "upload");
+  zero_ = false;
+  dev_valid_ = true;
+  host_valid_ = false;
+}
+
+void Storage::init_from_pointer(const double *values, size_t n) {
+  size_ = n;
+  ensure_device_buffer();
+  check(mg_upload(dev_, values, n), "upload");
+  zero_ = false;
+  dev_valid_ = true;
+  host_valid_ = false;
+}
+
+void Storage::sync_device_from_host() {
+  ensure_device_buffer();
+  check(mg_upload(dev_, host_.data(), size_), "upload");
+  dev_valid_ = true;
+}
+
+void Storage::sync_host_from_device() {
+  host_.resize(size_);
+  check(mg_download(host_.data(), dev_, size_), "download");
+  host_valid_ = true;
+}
+
+const double *Storage::device_read() {
+  if (zero_) {
+    ensure_device_buffer();
+    check(mg_fill(dev_, 0.0, size_), "fill");
+    zero_ = false;
+    dev_valid_ = true;
+    host_valid_ = false;
+  } else if (!dev_valid_) {
+    sync_device_from_host();
+  }
+  return dev_;
+}
+
+double *Storage::device_overwrite() {
+  ensure_device_buffer();
+  zero_ = false;
+  dev_valid_ = true;
+  host_valid_ = false;
+  return dev_;
+}
+
+double *Storage::device_accumulate(bool *store) {
+  if (zero_) {
+    ensure_device_buffer();
+    *store = true;
+    zero_ = false;
+    dev_valid_ = true;
+    host_valid_ = false;
+    return dev_;
+  }
+  *store = false;
+  if (!dev_valid_) {
+    sync_device_from_host();
+  }
+  host_valid_ = false;
+  return dev_;
+}
+
+double *Storage::device_update() {
+  device_read();
+  host_valid_ = false;
+  return dev_;
+}
+
+void Storage::set_zero() {
+  zero_ = true;
+  dev_valid_ = false;
+  host_valid_ = false;
+}
+
+void Storage::fill(double value) {
+  ensure_device_buffer();
+  check(mg_fill(dev_, value, size_), "fill");
+  zero_ = false;
+  dev_valid_ = true;
+  host_valid_ = false;
+}
+
+std::vector<double> &Storage::host_mutable() {
+  host_const();
+  // The caller may write through the reference at any later time, so the host
+  // vector is the authority until a kernel needs the values again.
+  dev_valid_ = false;
+  return host_;
+}
+
+const std::vector<double> &Storage::host_const() {
+  if (zero_) {
+    host_.assign(size_, 0.0);
+    zero_ = false;
+    host_valid_ = true;
+    dev_valid_ = false;
+  } else if (!host_valid_) {
+    sync_host_from_device();
+  }
+  return host_;
+}
+
+double Storage::peek(size_t index) {
+  if (zero_ || index >= size_) {
+    return 0.0;
+  }
+  if (host_valid_) {
+    return host_[index];
+  }
+  double v = 0.0;
+  check(mg_download(&v, dev_ + index, 1), "download");
+  return v;
+}
+
+void Storage::rehome(double *slice, std::shared_ptr<void> keepalive) {
+  if (!zero_) {
+    if (dev_valid_) {
+      check(mg_copy(slice, dev_, size_), "copy");
+    } else {
+      check(mg_upload(slice, host_.data(), size_), "upload");
+      dev_valid_ = true;
+    }
+  }
+  if (dev_ && owns_dev_) {
+    check(mg_free(dev_), "free");
+  }
+  dev_ = slice;
+  owns_dev_ = false;
+  keepalive_ = std::move(keepalive);
+}
+
+DeviceInts::DeviceInts(const int *host_values, size_t n) : n_(n) {
+  check(mg_alloc_i32(n, &dev_), "device allocation");
+  check(mg_upload_i32(dev_, host_values, n), "upload");
+}
+
+DeviceInts::DeviceInts(size_t n) : n_(n) { check(mg_alloc_i32(n, &dev_), "device allocation"); }
+
+DeviceInts::~DeviceInts() {
+  if (dev_) {
+    mg_free_i32(dev_);
+  }
+}
+
+}  // namespace micrograd::detail

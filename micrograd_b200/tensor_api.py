@@ -76,8 +76,11 @@ def _declare(lib, extensions: bool) -> None:
     if extensions:
         sigs.update({
             "mgt_sum_axis": (vp, [vp, C.c_int]),
-            "mgt_softmax_cross_entropy": (vp, [vp, vp]),
-            "mgt_softmax_cross_entropy_host": (vp, [vp, _c_int_p, C.c_size_t]),
+            "mgt_softmax_cross_entropy": (vp, [vp, vp, C.c_double]),
+            "mgt_softmax_cross_entropy_host": (vp, [vp, _c_int_p, C.c_size_t, C.c_double]),
+            "mgt_new_from_host": (vp, [_c_size_p, C.c_size_t, C.c_void_p]),
+            "mgt_comm_rank": (C.c_int, []),
+            "mgt_comm_world": (C.c_int, []),
             "mgt_argmax_rows": (C.c_int, [vp, _c_int_p, C.c_size_t]),
             "mgt_linear_forward_relu": (vp, [vp, vp]),
             "mgt_set_requires_grad": (C.c_int, [vp, C.c_int]),
@@ -285,13 +288,19 @@ def bind(path: str) -> SimpleNamespace:
     def format_scalar(op: str, scalar: float) -> str:
         return _take_str(lib.mgt_format_scalar(op.encode(), float(scalar)))
 
-    def softmax_cross_entropy(logits: Tensor, labels) -> Tensor:
-        """labels: a Tensor of class ids (one per row) or a host int array."""
+    def softmax_cross_entropy(logits: Tensor, labels, denom: float = 0.0) -> Tensor:
+        """labels: a Tensor of class ids (one per row) or a host int array.
+        denom: divisor of the mean (0 = rows; a shard passes the global batch)."""
         if isinstance(labels, Tensor):
-            return Tensor._wrap(lib.mgt_softmax_cross_entropy(logits._h, labels._h))
+            return Tensor._wrap(lib.mgt_softmax_cross_entropy(logits._h, labels._h, float(denom)))
         ids = np.ascontiguousarray(labels, dtype=np.int32).reshape(-1)
         return Tensor._wrap(lib.mgt_softmax_cross_entropy_host(
-            logits._h, ids.ctypes.data_as(_c_int_p), ids.size))
+            logits._h, ids.ctypes.data_as(_c_int_p), ids.size, float(denom)))
+
+    def from_host(shape, pointer: int) -> Tensor:
+        """Tensor::from_host: upload from a raw host address (e.g. pinned memory)."""
+        shp = (C.c_size_t * len(shape))(*[int(s) for s in shape])
+        return Tensor._wrap(lib.mgt_new_from_host(shp, len(shape), C.c_void_p(pointer)))
 
     def argmax_rows(x: Tensor) -> np.ndarray:
         rows = x.shape()[0]
@@ -315,7 +324,8 @@ def bind(path: str) -> SimpleNamespace:
         lib=lib, extensions=extensions, Tensor=Tensor, Linear=Linear, SGD=SGD,
         mse_loss=mse_loss, avg_pool_2x2=avg_pool_2x2, save_model=save_model,
         load_model=load_model, format_scalar=format_scalar,
-        softmax_cross_entropy=softmax_cross_entropy, argmax_rows=argmax_rows,
+        softmax_cross_entropy=softmax_cross_entropy, argmax_rows=argmax_rows, from_host=from_host,
+        comm_rank=lambda: int(lib.mgt_comm_rank()), comm_world=lambda: int(lib.mgt_comm_world()),
         synchronize=synchronize, comm_unique_id=comm_unique_id, comm_init=comm_init,
         comm_shutdown=comm_shutdown,
     )
