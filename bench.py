@@ -194,6 +194,17 @@ def run_product(args):
     abi.mg_check_kernel_status()
     del x_dev, y_dev, loss
 
+    if args.value_only:
+        if world > 1:
+            api.comm_shutdown()
+            dist.destroy_process_group()
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": batch * args.steps / (total_ms * 1e-3),
+                              "unit": "samples/s", "n_gpus": world, "steps": args.steps,
+                              "ms_per_step": total_ms / args.steps, "gpu_launches": int(launches),
+                              "config": {"global_batch": batch, "value_only": True}}), flush=True)
+        return
+
     # ---- e2e: host batches through the public API ----
     nbytes = rows * SIZES[0] * 8
     pinned = C.c_void_p()
@@ -361,6 +372,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch (default: config 4)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--value-only", action="store_true",
+                    help="run only the device-resident leg (for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
