@@ -101,6 +101,27 @@ int mg_add_row_fwd(const double *x, const double *row, double *out, size_t M, si
 /* gx[M,N] += g ; grow[N] += column sums of g.  Either may be NULL. */
 int mg_add_row_bwd(const double *g, double *gx, double *grow, size_t M, size_t N, int flags);
 
+/* Column sums of g[M,N] into out_row[N] (out_row += if accumulate != 0) — the bias
+ * gradient — for callers that must not allocate device memory when they need it:
+ * a latency-critical loop where an allocation would stall the device, a process
+ * whose memory belongs in full to another component's pool, a host framework that
+ * forbids allocation between its own synchronisation points.  This entry point has
+ * no counterpart in the reference.  It calls no cudaMalloc/cudaFree and no
+ * allocating library routine; the partial sums of the two-stage reduction live in
+ * a fixed 1 MiB array inside the library's device image (each GPU that loads the
+ * library holds it until the process exits).
+ *   - mg_init() must have run earlier, at set-up time (it allocates); this entry
+ *     point never initialises implicitly and fails with MG_ERR_INVALID otherwise.
+ *   - The first call on a device looks up the array's device address; make that
+ *     first call before starting any stream capture.
+ *   - Limit: N <= 131072 columns (any M); more is rejected with MG_ERR_INVALID and
+ *     a message naming the pooled alternative, mg_add_row_bwd(g, NULL, out_row, ..).
+ *   - All calls share the one array.  Each call overwrites every partial it later
+ *     reads, so stale contents never matter, but two calls that overlap on the GPU
+ *     (other streams, other threads) race on it: keep calls on the library's
+ *     ordered compute stream, one at a time. */
+int mg_colsum_noalloc(const double *g, double *out_row, size_t M, size_t N, int accumulate);
+
 /* ---- reductions --------------------------------------------------------- */
 /* Full sum: src/ops/Reduction.cpp:17-21 (forward), :26-30 (backward, the
  * scalar g[0] is read on the device).  Fixed-shape two-level tree, so the

@@ -56,6 +56,7 @@ SIGNATURES = {
                                C.c_void_p, _sz, C.c_int]),
     "mg_add_row_fwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, _sz, _sz]),
     "mg_add_row_bwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, _sz, _sz, C.c_int]),
+    "mg_colsum_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, _sz, _sz, C.c_int]),
     "mg_sum_all_fwd": (C.c_int, [C.c_void_p, C.c_void_p, _sz]),
     "mg_sum_all_bwd": (C.c_int, [C.c_void_p, C.c_void_p, _sz, C.c_int]),
     "mg_sum_lastaxis_fwd": (C.c_int, [C.c_void_p, C.c_void_p, _sz, _sz]),

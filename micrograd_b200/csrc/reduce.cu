@@ -429,3 +429,100 @@ int mg_argmax_rows(const double *x, int *out, size_t M, size_t N) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Column sum without any allocation.
+//
+// Some callers must not allocate device memory at the moment they need a bias
+// gradient: code running inside a latency-critical loop where a cudaMalloc
+// would stall the whole device, a process whose memory has been handed in full
+// to another component's pool, or a host framework that forbids allocation
+// between two of its own synchronisation points.  For them the partial sums of
+// the two-stage column reduction live in a fixed array in the library's own
+// device image instead of in pool memory.  Each GPU that loads the library
+// carries that array (1 MiB) until the process exits.
+//
+// Inside host code the array's name is only a handle for the runtime; it is not
+// a device address.  The address is looked up once per device with
+// cudaGetSymbolAddress, with that device current, and handed to the kernels.
+// ---------------------------------------------------------------------------
+namespace mg {
+
+constexpr size_t kNoAllocScratchElems = (size_t)1 << 17;  // 131072 doubles = 1 MiB
+constexpr int kNoAllocMaxDevices = 64;
+
+static __device__ __align__(256) double g_noalloc_colsum_scratch[kNoAllocScratchElems];
+static double *g_noalloc_scratch_addr[kNoAllocMaxDevices];  // per device, filled on first use
+
+// Device address of the static scratch on the current device (looked up once).
+static int noalloc_scratch(double **out) {
+  int device = -1;
+  MG_CUDA_TRY(cudaGetDevice(&device));
+  if (device < 0 || device >= kNoAllocMaxDevices)
+    return fail(MG_ERR_INVALID, "mg_colsum_noalloc: device ordinal %d not supported", device);
+  if (!g_noalloc_scratch_addr[device]) {
+    double *ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void **)&ptr, g_noalloc_colsum_scratch);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static column-sum scratch)");
+    if (!ptr) return fail(MG_ERR_CUDA, "mg_colsum_noalloc: static scratch has no device address");
+    g_noalloc_scratch_addr[device] = ptr;
+  }
+  *out = g_noalloc_scratch_addr[device];
+  return MG_OK;
+}
+
+}  // namespace mg
+
+extern "C" int mg_colsum_noalloc(const double *g, double *out_row, size_t M, size_t N,
+                                 int accumulate) {
+  // No implicit initialisation here: bringing the context up allocates.
+  Context &c = ctx();
+  if (!c.ready)
+    return fail(MG_ERR_INVALID,
+                "mg_colsum_noalloc: call mg_init() during set-up; this entry point never allocates");
+  if (M == 0 || N == 0) return MG_OK;
+  if (!g || !out_row) return fail(MG_ERR_INVALID, "mg_colsum_noalloc: null pointer");
+  if (N > kNoAllocScratchElems)
+    return fail(MG_ERR_INVALID,
+                "mg_colsum_noalloc: %zu columns exceed the static scratch limit of %zu; use "
+                "mg_add_row_bwd, which takes its scratch from the pool",
+                N, kNoAllocScratchElems);
+  double *scratch = nullptr;
+  int rc = noalloc_scratch(&scratch);
+  if (rc != MG_OK) return rc;
+
+  const bool vec = (N % 2 == 0) && (reinterpret_cast<uintptr_t>(g) & 15) == 0;
+  const size_t ncol = vec ? N / 2 : N;
+  const int TX = ncol >= 32 ? 32 : 8;
+  const int TY = 256 / TX;
+  const size_t gridx = (ncol + TX - 1) / TX;
+  // Row chunks as in the pooled path, capped so that S x N partials fit the array.
+  size_t S = (size_t)(148 * 4) / gridx;
+  const size_t max_rows = (M + (size_t)TY * 4 - 1) / ((size_t)TY * 4);
+  const size_t max_fit = kNoAllocScratchElems / N;
+  if (S > max_rows) S = max_rows;
+  if (S > max_fit) S = max_fit;
+  if (S < 1) S = 1;
+  if (S > 65535) S = 65535;
+  const size_t rows_per_chunk = (M + S - 1) / S;
+  S = (M + rows_per_chunk - 1) / rows_per_chunk;
+  // Every partial that stage 2 reads is written by stage 1 of the same call, so
+  // nothing left in the array by an earlier call can leak into this result.
+  dim3 grid((unsigned)gridx, (unsigned)S);
+  if (vec) {
+    if (TX == 32)
+      colsum_partial_kernel<2, 32><<<grid, 256, 0, c.stream>>>(g, nullptr, false, scratch, M, N, rows_per_chunk);
+    else
+      colsum_partial_kernel<2, 8><<<grid, 256, 0, c.stream>>>(g, nullptr, false, scratch, M, N, rows_per_chunk);
+  } else {
+    if (TX == 32)
+      colsum_partial_kernel<1, 32><<<grid, 256, 0, c.stream>>>(g, nullptr, false, scratch, M, N, rows_per_chunk);
+    else
+      colsum_partial_kernel<1, 8><<<grid, 256, 0, c.stream>>>(g, nullptr, false, scratch, M, N, rows_per_chunk);
+  }
+  MG_LAUNCH_CHECK("colsum_partial (static scratch)");
+  colsum_finish_kernel<<<(unsigned)((N + 255) / 256), 256, 0, c.stream>>>(scratch, S, N, out_row,
+                                                                          accumulate != 0);
+  MG_LAUNCH_CHECK("colsum_finish (static scratch)");
+  return MG_OK;
+}
