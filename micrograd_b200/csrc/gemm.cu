@@ -26,6 +26,7 @@
 #include "tma.cuh"
 
 #include <cstdlib>
+#include <type_traits>
 
 namespace mg {
 
@@ -71,7 +72,9 @@ __device__ __forceinline__ double2 apply_epilogue(double2 v, const GemmEpilogue 
 }
 
 // SHAPE: 0 m8n8k4, 1 m16n8k4, 2 m16n8k8, 3 m16n8k16.
-template <bool A_KCONTIG, bool B_KCONTIG, int SHAPE>
+// EDGE: the problem has ragged tiles (M or N not a multiple of 128); only then is
+// the per-sub-tile skipping compiled in, so the interior-only kernel stays lean.
+template <bool A_KCONTIG, bool B_KCONTIG, int SHAPE, bool EDGE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                  GemmEpilogue ep, int M, int N, int K, int tiles_n, int kt_per_split,
@@ -151,12 +154,23 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
 #pragma unroll
         for (int r = 0; r < 4; r++) acc[i][j][r] = 0.0;
 
+    // Edge tiles: number of 16-row / 8-column sub-tiles of this warp that hold at
+    // least one in-range output.  Out-of-range sub-tiles are skipped entirely (no
+    // fragment loads, no MMAs), so a ragged edge — 784 rows, or the 10 logit columns
+    // — costs what it contains, not a full 128-wide tile.  Both counts are
+    // warp-uniform.
+    const int m_left = M - (m0 + wm), n_left = N - (n0 + wn);
+    const int mt_count = m_left <= 0 ? 0 : (m_left >= 64 ? 4 : (m_left + 15) >> 4);
+    const int nt_count = n_left <= 0 ? 0 : (n_left >= 32 ? 4 : (n_left + 7) >> 3);
+
     // Loads the fragment pair (k = 2c, 2c+1) for the rows/cols this thread owns.
-    auto load_a = [&](const uint8_t *As, int slab, double2 (&lo)[4], double2 (&hi)[4]) {
+    auto load_a = [&](auto full, const uint8_t *As, int slab, double2 (&lo)[4], double2 (&hi)[4]) {
+      constexpr bool FULL = decltype(full)::value;
       const int c = c0 ^ slab;
       if (A_KCONTIG) {
 #pragma unroll
         for (int mt = 0; mt < 4; mt++) {
+          if (!FULL && mt >= mt_count) continue;
           const int off = (wm + mt * 16 + g) * 128 + ((c ^ g) << 4);
           lo[mt] = *reinterpret_cast<const double2 *>(As + off);
           hi[mt] = *reinterpret_cast<const double2 *>(As + off + 8 * 128);
@@ -165,6 +179,7 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         const int ka = 2 * c, kb = 2 * c + 1;
 #pragma unroll
         for (int mt = 0; mt < 4; mt++) {
+          if (!FULL && mt >= mt_count) continue;
           const int base = ((wm >> 4) + mt) * 2048;
           const int mlo = g, mhi = g + 8;
           lo[mt].x = *reinterpret_cast<const double *>(
@@ -178,11 +193,13 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         }
       }
     };
-    auto load_b = [&](const uint8_t *Bs, int slab, double2 (&b)[4]) {
+    auto load_b = [&](auto full, const uint8_t *Bs, int slab, double2 (&b)[4]) {
+      constexpr bool FULL = decltype(full)::value;
       const int c = c0 ^ slab;
       if (B_KCONTIG) {
 #pragma unroll
         for (int nt = 0; nt < 4; nt++) {
+          if (!FULL && nt >= nt_count) continue;
           const int off = (wn + nt * 8 + g) * 128 + ((c ^ g) << 4);
           b[nt] = *reinterpret_cast<const double2 *>(Bs + off);
         }
@@ -190,6 +207,7 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         const int ka = 2 * c, kb = 2 * c + 1;
 #pragma unroll
         for (int nt = 0; nt < 4; nt++) {
+          if (!FULL && nt >= nt_count) continue;
           const int nl = wn + nt * 8 + g;
           const int base = (nl >> 4) * 2048, nn = nl & 15;
           b[nt].x = *reinterpret_cast<const double *>(
@@ -200,37 +218,34 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
       }
     };
 
-    bool ok = true;
-    for (int it = 0; it < nkt; ++it) {
-      const int s = it % kStages;
-      if (!mbar_wait_bounded(smem_u32(full_bar + s), (it / kStages) & 1, abort_flag)) {
-        ok = false;
-        break;
-      }
-      const uint8_t *As = smem + s * kStageBytes;
-      const uint8_t *Bs = As + kTileBytes;
+    // One 16-deep stage of MMAs.  FULL: every sub-tile is live (interior tiles).
+    auto compute_stage = [&](auto full, const uint8_t *As, const uint8_t *Bs) {
+      constexpr bool FULL = decltype(full)::value;
       if (SHAPE == 3) {
         double2 lo0[4], hi0[4], b0[4], lo1[4], hi1[4], b1[4];
-        load_a(As, 0, lo0, hi0);
-        load_b(Bs, 0, b0);
-        load_a(As, 1, lo1, hi1);
-        load_b(Bs, 1, b1);
+        load_a(full, As, 0, lo0, hi0);
+        load_b(full, Bs, 0, b0);
+        load_a(full, As, 1, lo1, hi1);
+        load_b(full, Bs, 1, b1);
 #pragma unroll
         for (int mt = 0; mt < 4; mt++)
 #pragma unroll
-          for (int nt = 0; nt < 4; nt++)
+          for (int nt = 0; nt < 4; nt++) {
+            if (!FULL && (mt >= mt_count || nt >= nt_count)) continue;
             dmma_m16n8k16(acc[mt][nt], lo0[mt].x, hi0[mt].x, lo0[mt].y, hi0[mt].y, lo1[mt].x,
                           hi1[mt].x, lo1[mt].y, hi1[mt].y, b0[nt].x, b0[nt].y, b1[nt].x, b1[nt].y);
+          }
       } else {
 #pragma unroll
         for (int slab = 0; slab < 2; slab++) {
           double2 lo[4], hi[4], b[4];
-          load_a(As, slab, lo, hi);
-          load_b(Bs, slab, b);
+          load_a(full, As, slab, lo, hi);
+          load_b(full, Bs, slab, b);
 #pragma unroll
           for (int mt = 0; mt < 4; mt++)
 #pragma unroll
             for (int nt = 0; nt < 4; nt++) {
+              if (!FULL && (mt >= mt_count || nt >= nt_count)) continue;
               if (SHAPE == 2) {
                 dmma_m16n8k8(acc[mt][nt], lo[mt].x, hi[mt].x, lo[mt].y, hi[mt].y, b[nt].x, b[nt].y);
               } else if (SHAPE == 1) {
@@ -244,6 +259,22 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
               }
             }
         }
+      }
+    };
+
+    bool ok = true;
+    for (int it = 0; it < nkt; ++it) {
+      const int s = it % kStages;
+      if (!mbar_wait_bounded(smem_u32(full_bar + s), (it / kStages) & 1, abort_flag)) {
+        ok = false;
+        break;
+      }
+      const uint8_t *As = smem + s * kStageBytes;
+      const uint8_t *Bs = As + kTileBytes;
+      if (!EDGE) {
+        compute_stage(std::true_type{}, As, Bs);
+      } else if (mt_count > 0 && nt_count > 0) {
+        compute_stage(std::false_type{}, As, Bs);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(empty_bar + s));
@@ -402,11 +433,12 @@ static int default_dmma_shape() {
   return 2;
 }
 
-template <bool AK, bool BK_, int SHAPE>
-static int launch_dmma(const CUtensorMap &ma, const CUtensorMap &mb, const GemmEpilogue &ep, int M,
-                       int N, int K, int tiles_m, int tiles_n, int splits, int kt_per_split) {
+template <bool AK, bool BK_, int SHAPE, bool EDGE>
+static int launch_dmma_edge(const CUtensorMap &ma, const CUtensorMap &mb, const GemmEpilogue &ep,
+                            int M, int N, int K, int tiles_m, int tiles_n, int splits,
+                            int kt_per_split) {
   static bool configured = false;
-  auto kernel = dmma_gemm_kernel<AK, BK_, SHAPE>;
+  auto kernel = dmma_gemm_kernel<AK, BK_, SHAPE, EDGE>;
   if (!configured) {
     MG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      kGemmSmemBytes));
@@ -418,6 +450,16 @@ static int launch_dmma(const CUtensorMap &ma, const CUtensorMap &mb, const GemmE
                                                             kt_per_split, c.kernel_status);
   MG_LAUNCH_CHECK("dmma_gemm");
   return MG_OK;
+}
+
+template <bool AK, bool BK_, int SHAPE>
+static int launch_dmma(const CUtensorMap &ma, const CUtensorMap &mb, const GemmEpilogue &ep, int M,
+                       int N, int K, int tiles_m, int tiles_n, int splits, int kt_per_split) {
+  if ((M % BM) != 0 || (N % BN) != 0)
+    return launch_dmma_edge<AK, BK_, SHAPE, true>(ma, mb, ep, M, N, K, tiles_m, tiles_n, splits,
+                                                  kt_per_split);
+  return launch_dmma_edge<AK, BK_, SHAPE, false>(ma, mb, ep, M, N, K, tiles_m, tiles_n, splits,
+                                                 kt_per_split);
 }
 
 template <bool AK, bool BK_>
