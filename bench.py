@@ -77,7 +77,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100", "-i", str(self.index)],
+                 "-lms", "200", "-i", str(self.index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -169,27 +169,47 @@ def run_product(args):
     x_dev = api.Tensor([rows, SIZES[0]], X)
     x_dev.set_requires_grad(False)
     y_dev = api.Tensor([rows], y.astype(np.float64))
-    for _ in range(args.warmup):
-        train_step(api, layers, opt, x_dev, y_dev, batch)
-    barrier()
+    # The clock sampler is started before the warm-up: the first NVML query of a
+    # new nvidia-smi process stalls kernel launches for tens of milliseconds, which
+    # must not land inside the timed region.
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        time.sleep(1.0)
+    for _ in range(args.warmup):
+        train_step(api, layers, opt, x_dev, y_dev, batch)
+    barrier()
+    if rank == 0:
+        sampler.rows.clear()          # keep only samples taken under the timed load
     launches0 = abi.mg_launch_count()
-    e0, e1 = C.c_int(), C.c_int()
-    abi.mg_event_create(C.byref(e0))
-    abi.mg_event_create(C.byref(e1))
-    abi.mg_event_record(e0.value)
+    # one event per step boundary: the total is first-to-last, the per-step
+    # spread shows whether a slow run was slow throughout
+    marks = []
+    for _ in range(args.steps + 1):
+        ev = C.c_int()
+        abi.mg_event_create(C.byref(ev))
+        marks.append(ev.value)
+    abi.mg_event_record(marks[0])
     loss = None
-    for _ in range(args.steps):
+    for i in range(args.steps):
         loss = train_step(api, layers, opt, x_dev, y_dev, batch)
-    abi.mg_event_record(e1.value)
+        if args.sync_each_step:
+            abi.mg_sync()
+        abi.mg_event_record(marks[i + 1])
     ms = C.c_float()
-    abi.mg_event_elapsed_ms(e0.value, e1.value, C.byref(ms))
+    abi.mg_event_elapsed_ms(marks[0], marks[-1], C.byref(ms))
+    per_step = []
+    for i in range(args.steps):
+        t = C.c_float()
+        abi.mg_event_elapsed_ms(marks[i], marks[i + 1], C.byref(t))
+        per_step.append(float(t.value))
+    for ev in marks:
+        abi.mg_event_destroy(ev)
     barrier()
     launches = abi.mg_launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
     total_ms = max_over_ranks(float(ms.value))
+    step_spread = {"min": min(per_step), "median": float(np.median(per_step)), "max": max(per_step)}
     final_loss = float(loss.data()[0])
     abi.mg_check_kernel_status()
     del x_dev, y_dev, loss
@@ -201,7 +221,8 @@ def run_product(args):
         if rank == 0:
             print(json.dumps({"metric": METRIC, "value": batch * args.steps / (total_ms * 1e-3),
                               "unit": "samples/s", "n_gpus": world, "steps": args.steps,
-                              "ms_per_step": total_ms / args.steps, "gpu_launches": int(launches),
+                              "ms_per_step": total_ms / args.steps, "ms_per_step_spread": step_spread,
+                              "gpu_launches": int(launches), "clocks": clocks,
                               "config": {"global_batch": batch, "value_only": True}}), flush=True)
         return
 
@@ -247,7 +268,8 @@ def run_product(args):
     value = batch * args.steps / (total_ms * 1e-3)
     out = {
         "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "ms_per_step_spread": step_spread,
+        "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
         "config": {"workload": "MLP 784-1024-1024-10 fp64 train step (BASELINE config 4)",
                    "global_batch": batch, "rows_per_gpu": rows, "lr": LR, "parallelism": f"dp{world}",
@@ -372,6 +394,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch (default: config 4)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sync-each-step", action="store_true",
+                    help="diagnostic: host waits for the device after every step")
     ap.add_argument("--value-only", action="store_true",
                     help="run only the device-resident leg (for profiler captures)")
     args = ap.parse_args()

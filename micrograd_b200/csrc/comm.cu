@@ -11,6 +11,7 @@
 #include <nccl.h>
 
 #include <chrono>
+#include <cstdlib>
 #include <cstring>
 #include <thread>
 
@@ -21,6 +22,7 @@ struct NcclApi {
   void *handle = nullptr;
   decltype(&ncclGetUniqueId) GetUniqueId = nullptr;
   decltype(&ncclCommInitRank) CommInitRank = nullptr;
+  decltype(&ncclCommInitRankConfig) CommInitRankConfig = nullptr;  // optional
   decltype(&ncclCommDestroy) CommDestroy = nullptr;
   decltype(&ncclCommAbort) CommAbort = nullptr;
   decltype(&ncclAllReduce) AllReduce = nullptr;
@@ -52,6 +54,8 @@ int load_nccl() {
   MG_NCCL_SYM(GetErrorString, ncclGetErrorString)
   MG_NCCL_SYM(CommGetAsyncError, ncclCommGetAsyncError)
 #undef MG_NCCL_SYM
+  g_nccl.CommInitRankConfig =
+      reinterpret_cast<decltype(g_nccl.CommInitRankConfig)>(dlsym(h, "ncclCommInitRankConfig"));
   g_nccl.handle = h;
   return MG_OK;
 }
@@ -90,7 +94,22 @@ int mg_comm_init(const char *id128_host, int rank, int world) {
   if (rc != MG_OK) return rc;
   ncclUniqueId id;
   std::memcpy(&id, id128_host, sizeof(id));
-  ncclResult_t r = g_nccl.CommInitRank(&g_comm, world, id, rank);
+  // The gradient messages are a few MB: a handful of CTAs moves them at NVLink
+  // speed, and every CTA NCCL takes is an SM the overlapped GEMMs lose.
+  int max_ctas = 8;
+  if (const char *v = std::getenv("MG_NCCL_MAX_CTAS")) {
+    if (*v) max_ctas = std::atoi(v);
+  }
+  ncclResult_t r;
+  if (g_nccl.CommInitRankConfig && max_ctas > 0) {
+    ncclConfig_t config = NCCL_CONFIG_INITIALIZER;
+    config.blocking = 1;
+    config.maxCTAs = max_ctas;
+    config.minCTAs = 1;
+    r = g_nccl.CommInitRankConfig(&g_comm, world, id, rank, &config);
+  } else {
+    r = g_nccl.CommInitRank(&g_comm, world, id, rank);
+  }
   if (r != ncclSuccess) {
     g_comm = nullptr;
     return nccl_fail(r, "ncclCommInitRank");

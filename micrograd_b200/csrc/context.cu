@@ -68,7 +68,12 @@ static int init_locked(int device) {
   c.device = device;
   c.sm_count = prop.multiProcessorCount;
   MG_CUDA_TRY(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
-  MG_CUDA_TRY(cudaStreamCreateWithFlags(&c.comm_stream, cudaStreamNonBlocking));
+  // The communication stream gets the highest priority: an all-reduce kernel is
+  // placed on the first SMs that free up instead of queueing behind every CTA of
+  // the GEMM in flight, so neither rank spins long waiting for its peer.
+  int prio_least = 0, prio_greatest = 0;
+  MG_CUDA_TRY(cudaDeviceGetStreamPriorityRange(&prio_least, &prio_greatest));
+  MG_CUDA_TRY(cudaStreamCreateWithPriority(&c.comm_stream, cudaStreamNonBlocking, prio_greatest));
   MG_CUDA_TRY(cudaEventCreateWithFlags(&c.fork_event, cudaEventDisableTiming));
   MG_CUDA_TRY(cudaEventCreateWithFlags(&c.join_event, cudaEventDisableTiming));
   // Keep freed blocks in the stream-ordered pool instead of returning them to

@@ -30,16 +30,35 @@
 
 namespace mg {
 
-constexpr int BM = 128, BN = 128, BK = 16;
-constexpr int kStages = 6;
+constexpr int BK = 16;  // contraction depth of one stage (one 128-byte swizzle row of doubles)
 constexpr int kConsumerWarps = 8;
 constexpr int kProducerWarps = 4;  // one warp group; only its first lane issues copies
 constexpr int kGemmThreads = (kConsumerWarps + kProducerWarps) * 32;  // 384
 // Register split between the warp groups (setmaxnreg): 8*32*232 + 4*32*40 <= 64 K.
 constexpr int kConsumerRegs = 232, kProducerRegs = 40;
-constexpr int kTileBytes = BM * BK * 8;       // 16 KB; A and B tiles are the same size
-constexpr int kStageBytes = 2 * kTileBytes;   // 32 KB
-constexpr int kGemmSmemBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 2 * kStages * 8;
+
+// CTA tile = (8 / WARPS_N) x WARPS_N consumer warps, each owning MT x NT
+// sub-tiles of 16 x 8 outputs.
+template <int WARPS_N_, int MT_, int NT_, int STAGES_>
+struct TileCfg {
+  static constexpr int WARPS_N = WARPS_N_, WARPS_M = kConsumerWarps / WARPS_N_;
+  static constexpr int MT = MT_, NT = NT_, STAGES = STAGES_;
+  static constexpr int BM = WARPS_M * MT * 16, BN = WARPS_N * NT * 8;
+  static constexpr int A_BYTES = BM * BK * 8, B_BYTES = BN * BK * 8;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 2 * STAGES * 8;
+  static_assert(A_BYTES % 1024 == 0 && B_BYTES % 1024 == 0, "swizzled tiles need 1 KB alignment");
+  static_assert(BM % 16 == 0 && BN % 16 == 0, "tiles are built from 16-wide TMA boxes");
+};
+// 128 x 128, six 32 KB stages: compute-bound shapes.
+using MainCfg = TileCfg<4, 4, 4, 6>;
+// 128 x 32, eight 20 KB stages: outputs at most 32 columns wide (the 10 logits).
+// All eight warps split the rows, so the MMAs spread over the four SM
+// sub-partitions instead of landing on the one that owns a single warp column.
+using SkinnyCfg = TileCfg<1, 1, 4, 8>;
+// 128 x 64, eight 24 KB stages: used when 128 x 128 tiles would leave the last
+// wave of CTAs mostly empty (e.g. 512 tiles on 148 SMs).
+using HalfCfg = TileCfg<2, 2, 4, 8>;
 
 struct GemmEpilogue {
   double *D;            // output [M][N]
@@ -71,14 +90,141 @@ __device__ __forceinline__ double2 apply_epilogue(double2 v, const GemmEpilogue 
   return v;
 }
 
+// Fragment pair (k = 2c, 2c+1) of the A operand for the MT row sub-tiles of a
+// warp: lo = rows g, hi = rows g + 8 of each 16-row sub-tile.
+template <bool KCONTIG, bool FULL, int MT>
+__device__ __forceinline__ void load_a_frags(const uint8_t *As, int c, int g, int wm, int mt_count,
+                                             double2 (&lo)[MT], double2 (&hi)[MT]) {
+  if (KCONTIG) {
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) {
+      if (!FULL && mt >= mt_count) continue;
+      const int off = (wm + mt * 16 + g) * 128 + ((c ^ g) << 4);
+      lo[mt] = *reinterpret_cast<const double2 *>(As + off);
+      hi[mt] = *reinterpret_cast<const double2 *>(As + off + 8 * 128);
+    }
+  } else {
+    const int ka = 2 * c, kb = 2 * c + 1;
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) {
+      if (!FULL && mt >= mt_count) continue;
+      const int base = ((wm >> 4) + mt) * 2048;
+      const int mlo = g, mhi = g + 8;
+      lo[mt].x = *reinterpret_cast<const double *>(
+          As + base + ka * 128 + ((((mlo >> 1) ^ (ka & 7))) << 4) + (mlo & 1) * 8);
+      lo[mt].y = *reinterpret_cast<const double *>(
+          As + base + kb * 128 + ((((mlo >> 1) ^ (kb & 7))) << 4) + (mlo & 1) * 8);
+      hi[mt].x = *reinterpret_cast<const double *>(
+          As + base + ka * 128 + ((((mhi >> 1) ^ (ka & 7))) << 4) + (mhi & 1) * 8);
+      hi[mt].y = *reinterpret_cast<const double *>(
+          As + base + kb * 128 + ((((mhi >> 1) ^ (kb & 7))) << 4) + (mhi & 1) * 8);
+    }
+  }
+}
+
+// Fragment pair of the B operand for the NT column sub-tiles of a warp (column g).
+template <bool KCONTIG, bool FULL, int NT>
+__device__ __forceinline__ void load_b_frags(const uint8_t *Bs, int c, int g, int wn, int nt_count,
+                                             double2 (&b)[NT]) {
+  if (KCONTIG) {
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+      if (!FULL && nt >= nt_count) continue;
+      const int off = (wn + nt * 8 + g) * 128 + ((c ^ g) << 4);
+      b[nt] = *reinterpret_cast<const double2 *>(Bs + off);
+    }
+  } else {
+    const int ka = 2 * c, kb = 2 * c + 1;
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+      if (!FULL && nt >= nt_count) continue;
+      const int nl = wn + nt * 8 + g;
+      const int base = (nl >> 4) * 2048, nn = nl & 15;
+      b[nt].x = *reinterpret_cast<const double *>(
+          Bs + base + ka * 128 + ((((nn >> 1) ^ (ka & 7))) << 4) + (nn & 1) * 8);
+      b[nt].y = *reinterpret_cast<const double *>(
+          Bs + base + kb * 128 + ((((nn >> 1) ^ (kb & 7))) << 4) + (nn & 1) * 8);
+    }
+  }
+}
+
+// One 16-deep stage of MMAs for a warp.  FULL: every sub-tile is live.
+template <bool A_KCONTIG, bool B_KCONTIG, int SHAPE, bool FULL, int MT, int NT>
+__device__ __forceinline__ void compute_stage(double (&acc)[MT][NT][4], const uint8_t *As,
+                                              const uint8_t *Bs, int c0, int g, int wm, int wn,
+                                              int mt_count, int nt_count) {
+  if (SHAPE == 3) {
+    double2 lo0[MT], hi0[MT], b0[NT], lo1[MT], hi1[MT], b1[NT];
+    load_a_frags<A_KCONTIG, FULL, MT>(As, c0, g, wm, mt_count, lo0, hi0);
+    load_b_frags<B_KCONTIG, FULL, NT>(Bs, c0, g, wn, nt_count, b0);
+    load_a_frags<A_KCONTIG, FULL, MT>(As, c0 ^ 1, g, wm, mt_count, lo1, hi1);
+    load_b_frags<B_KCONTIG, FULL, NT>(Bs, c0 ^ 1, g, wn, nt_count, b1);
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++) {
+        if (!FULL && (mt >= mt_count || nt >= nt_count)) continue;
+        dmma_m16n8k16(acc[mt][nt], lo0[mt].x, hi0[mt].x, lo0[mt].y, hi0[mt].y, lo1[mt].x, hi1[mt].x,
+                      lo1[mt].y, hi1[mt].y, b0[nt].x, b0[nt].y, b1[nt].x, b1[nt].y);
+      }
+  } else {
+#pragma unroll
+    for (int slab = 0; slab < 2; slab++) {
+      double2 lo[MT], hi[MT], b[NT];
+      load_a_frags<A_KCONTIG, FULL, MT>(As, c0 ^ slab, g, wm, mt_count, lo, hi);
+      load_b_frags<B_KCONTIG, FULL, NT>(Bs, c0 ^ slab, g, wn, nt_count, b);
+#pragma unroll
+      for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+          if (!FULL && (mt >= mt_count || nt >= nt_count)) continue;
+          if (SHAPE == 2) {
+            dmma_m16n8k8(acc[mt][nt], lo[mt].x, hi[mt].x, lo[mt].y, hi[mt].y, b[nt].x, b[nt].y);
+          } else if (SHAPE == 1) {
+            dmma_m16n8k4(acc[mt][nt], lo[mt].x, hi[mt].x, b[nt].x);
+            dmma_m16n8k4(acc[mt][nt], lo[mt].y, hi[mt].y, b[nt].y);
+          } else {
+            dmma_m8n8k4(acc[mt][nt][0], acc[mt][nt][1], lo[mt].x, b[nt].x);
+            dmma_m8n8k4(acc[mt][nt][2], acc[mt][nt][3], hi[mt].x, b[nt].x);
+            dmma_m8n8k4(acc[mt][nt][0], acc[mt][nt][1], lo[mt].y, b[nt].y);
+            dmma_m8n8k4(acc[mt][nt][2], acc[mt][nt][3], hi[mt].y, b[nt].y);
+          }
+        }
+    }
+  }
+}
+
+// Consumer side of the stage ring: wait for a stage, run its MMAs, hand the
+// stage back.  Returns false if a bounded wait gave up.
+template <bool A_KCONTIG, bool B_KCONTIG, int SHAPE, bool FULL, class Cfg>
+__device__ __forceinline__ bool consumer_loop(double (&acc)[Cfg::MT][Cfg::NT][4], const uint8_t *smem,
+                                              uint64_t *full_bar, uint64_t *empty_bar, int nkt,
+                                              volatile int *abort_flag, int c0, int g, int wm, int wn,
+                                              int lane, int mt_count, int nt_count) {
+  for (int it = 0; it < nkt; ++it) {
+    const int s = it % Cfg::STAGES;
+    if (!mbar_wait_bounded(smem_u32(full_bar + s), (it / Cfg::STAGES) & 1, abort_flag)) return false;
+    const uint8_t *As = smem + s * Cfg::STAGE_BYTES;
+    const uint8_t *Bs = As + Cfg::A_BYTES;
+    if (FULL || (mt_count > 0 && nt_count > 0))
+      compute_stage<A_KCONTIG, B_KCONTIG, SHAPE, FULL, Cfg::MT, Cfg::NT>(acc, As, Bs, c0, g, wm, wn,
+                                                                         mt_count, nt_count);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(empty_bar + s));
+  }
+  return true;
+}
+
 // SHAPE: 0 m8n8k4, 1 m16n8k4, 2 m16n8k8, 3 m16n8k16.
 // EDGE: the problem has ragged tiles (M or N not a multiple of 128); only then is
 // the per-sub-tile skipping compiled in, so the interior-only kernel stays lean.
-template <bool A_KCONTIG, bool B_KCONTIG, int SHAPE, bool EDGE>
+template <bool A_KCONTIG, bool B_KCONTIG, int SHAPE, bool EDGE, class Cfg>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                  GemmEpilogue ep, int M, int N, int K, int tiles_n, int kt_per_split,
                  int *status) {
+  constexpr int BM = Cfg::BM, BN = Cfg::BN, MT = Cfg::MT, NT = Cfg::NT;
+  constexpr int kStages = Cfg::STAGES, kStageBytes = Cfg::STAGE_BYTES, kTileBytes = Cfg::A_BYTES;
   extern __shared__ uint8_t smem_raw[];
   __shared__ int abort_flag_s;
   volatile int *abort_flag = &abort_flag_s;
@@ -141,16 +287,16 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     // ---------------- consumer warp groups ----------------
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kConsumerRegs));
     const int g = lane >> 2, t = lane & 3;
-    const int wm = (warp >> 2) * 64, wn = (warp & 3) * 32;
+    const int wm = (warp / Cfg::WARPS_N) * (MT * 16), wn = (warp % Cfg::WARPS_N) * (NT * 8);
     // 16-byte chunk owned by this thread in the first half-slab; the second
     // half-slab uses chunk ^ 1.
     const int c0 = (t << 1) | (__popc(t) & 1);
 
-    double acc[4][4][4];
+    double acc[MT][NT][4];
 #pragma unroll
-    for (int i = 0; i < 4; i++)
+    for (int i = 0; i < MT; i++)
 #pragma unroll
-      for (int j = 0; j < 4; j++)
+      for (int j = 0; j < NT; j++)
 #pragma unroll
         for (int r = 0; r < 4; r++) acc[i][j][r] = 0.0;
 
@@ -160,137 +306,33 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     // — costs what it contains, not a full 128-wide tile.  Both counts are
     // warp-uniform.
     const int m_left = M - (m0 + wm), n_left = N - (n0 + wn);
-    const int mt_count = m_left <= 0 ? 0 : (m_left >= 64 ? 4 : (m_left + 15) >> 4);
-    const int nt_count = n_left <= 0 ? 0 : (n_left >= 32 ? 4 : (n_left + 7) >> 3);
+    const int mt_count = m_left <= 0 ? 0 : (m_left >= MT * 16 ? MT : (m_left + 15) >> 4);
+    const int nt_count = n_left <= 0 ? 0 : (n_left >= NT * 8 ? NT : (n_left + 7) >> 3);
 
-    // Loads the fragment pair (k = 2c, 2c+1) for the rows/cols this thread owns.
-    auto load_a = [&](auto full, const uint8_t *As, int slab, double2 (&lo)[4], double2 (&hi)[4]) {
-      constexpr bool FULL = decltype(full)::value;
-      const int c = c0 ^ slab;
-      if (A_KCONTIG) {
-#pragma unroll
-        for (int mt = 0; mt < 4; mt++) {
-          if (!FULL && mt >= mt_count) continue;
-          const int off = (wm + mt * 16 + g) * 128 + ((c ^ g) << 4);
-          lo[mt] = *reinterpret_cast<const double2 *>(As + off);
-          hi[mt] = *reinterpret_cast<const double2 *>(As + off + 8 * 128);
-        }
-      } else {
-        const int ka = 2 * c, kb = 2 * c + 1;
-#pragma unroll
-        for (int mt = 0; mt < 4; mt++) {
-          if (!FULL && mt >= mt_count) continue;
-          const int base = ((wm >> 4) + mt) * 2048;
-          const int mlo = g, mhi = g + 8;
-          lo[mt].x = *reinterpret_cast<const double *>(
-              As + base + ka * 128 + ((((mlo >> 1) ^ (ka & 7))) << 4) + (mlo & 1) * 8);
-          lo[mt].y = *reinterpret_cast<const double *>(
-              As + base + kb * 128 + ((((mlo >> 1) ^ (kb & 7))) << 4) + (mlo & 1) * 8);
-          hi[mt].x = *reinterpret_cast<const double *>(
-              As + base + ka * 128 + ((((mhi >> 1) ^ (ka & 7))) << 4) + (mhi & 1) * 8);
-          hi[mt].y = *reinterpret_cast<const double *>(
-              As + base + kb * 128 + ((((mhi >> 1) ^ (kb & 7))) << 4) + (mhi & 1) * 8);
-        }
-      }
-    };
-    auto load_b = [&](auto full, const uint8_t *Bs, int slab, double2 (&b)[4]) {
-      constexpr bool FULL = decltype(full)::value;
-      const int c = c0 ^ slab;
-      if (B_KCONTIG) {
-#pragma unroll
-        for (int nt = 0; nt < 4; nt++) {
-          if (!FULL && nt >= nt_count) continue;
-          const int off = (wn + nt * 8 + g) * 128 + ((c ^ g) << 4);
-          b[nt] = *reinterpret_cast<const double2 *>(Bs + off);
-        }
-      } else {
-        const int ka = 2 * c, kb = 2 * c + 1;
-#pragma unroll
-        for (int nt = 0; nt < 4; nt++) {
-          if (!FULL && nt >= nt_count) continue;
-          const int nl = wn + nt * 8 + g;
-          const int base = (nl >> 4) * 2048, nn = nl & 15;
-          b[nt].x = *reinterpret_cast<const double *>(
-              Bs + base + ka * 128 + ((((nn >> 1) ^ (ka & 7))) << 4) + (nn & 1) * 8);
-          b[nt].y = *reinterpret_cast<const double *>(
-              Bs + base + kb * 128 + ((((nn >> 1) ^ (kb & 7))) << 4) + (nn & 1) * 8);
-        }
-      }
-    };
-
-    // One 16-deep stage of MMAs.  FULL: every sub-tile is live (interior tiles).
-    auto compute_stage = [&](auto full, const uint8_t *As, const uint8_t *Bs) {
-      constexpr bool FULL = decltype(full)::value;
-      if (SHAPE == 3) {
-        double2 lo0[4], hi0[4], b0[4], lo1[4], hi1[4], b1[4];
-        load_a(full, As, 0, lo0, hi0);
-        load_b(full, Bs, 0, b0);
-        load_a(full, As, 1, lo1, hi1);
-        load_b(full, Bs, 1, b1);
-#pragma unroll
-        for (int mt = 0; mt < 4; mt++)
-#pragma unroll
-          for (int nt = 0; nt < 4; nt++) {
-            if (!FULL && (mt >= mt_count || nt >= nt_count)) continue;
-            dmma_m16n8k16(acc[mt][nt], lo0[mt].x, hi0[mt].x, lo0[mt].y, hi0[mt].y, lo1[mt].x,
-                          hi1[mt].x, lo1[mt].y, hi1[mt].y, b0[nt].x, b0[nt].y, b1[nt].x, b1[nt].y);
-          }
-      } else {
-#pragma unroll
-        for (int slab = 0; slab < 2; slab++) {
-          double2 lo[4], hi[4], b[4];
-          load_a(full, As, slab, lo, hi);
-          load_b(full, Bs, slab, b);
-#pragma unroll
-          for (int mt = 0; mt < 4; mt++)
-#pragma unroll
-            for (int nt = 0; nt < 4; nt++) {
-              if (!FULL && (mt >= mt_count || nt >= nt_count)) continue;
-              if (SHAPE == 2) {
-                dmma_m16n8k8(acc[mt][nt], lo[mt].x, hi[mt].x, lo[mt].y, hi[mt].y, b[nt].x, b[nt].y);
-              } else if (SHAPE == 1) {
-                dmma_m16n8k4(acc[mt][nt], lo[mt].x, hi[mt].x, b[nt].x);
-                dmma_m16n8k4(acc[mt][nt], lo[mt].y, hi[mt].y, b[nt].y);
-              } else {
-                dmma_m8n8k4(acc[mt][nt][0], acc[mt][nt][1], lo[mt].x, b[nt].x);
-                dmma_m8n8k4(acc[mt][nt][2], acc[mt][nt][3], hi[mt].x, b[nt].x);
-                dmma_m8n8k4(acc[mt][nt][0], acc[mt][nt][1], lo[mt].y, b[nt].y);
-                dmma_m8n8k4(acc[mt][nt][2], acc[mt][nt][3], hi[mt].y, b[nt].y);
-              }
-            }
-        }
-      }
-    };
-
-    bool ok = true;
-    for (int it = 0; it < nkt; ++it) {
-      const int s = it % kStages;
-      if (!mbar_wait_bounded(smem_u32(full_bar + s), (it / kStages) & 1, abort_flag)) {
-        ok = false;
-        break;
-      }
-      const uint8_t *As = smem + s * kStageBytes;
-      const uint8_t *Bs = As + kTileBytes;
-      if (!EDGE) {
-        compute_stage(std::true_type{}, As, Bs);
-      } else if (mt_count > 0 && nt_count > 0) {
-        compute_stage(std::false_type{}, As, Bs);
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(empty_bar + s));
+    // Interior tiles of a ragged problem run the same unguarded loop as a problem
+    // without edges; only the CTAs on the ragged border pay for the guards.
+    bool ok;
+    if (!EDGE || (mt_count == MT && nt_count == NT)) {
+      ok = consumer_loop<A_KCONTIG, B_KCONTIG, SHAPE, true, Cfg>(acc, smem, full_bar, empty_bar, nkt,
+                                                                  abort_flag, c0, g, wm, wn, lane,
+                                                                  MT, NT);
+    } else {
+      ok = consumer_loop<A_KCONTIG, B_KCONTIG, SHAPE, false, Cfg>(acc, smem, full_bar, empty_bar,
+                                                                   nkt, abort_flag, c0, g, wm, wn,
+                                                                   lane, mt_count, nt_count);
     }
 
     if (ok) {
       // ---------------- epilogue ----------------
       double *dst = ep.partial ? ep.partial + (size_t)blockIdx.z * (size_t)M * (size_t)N : ep.D;
 #pragma unroll
-      for (int mt = 0; mt < 4; mt++) {
+      for (int mt = 0; mt < MT; mt++) {
 #pragma unroll
         for (int h = 0; h < 2; h++) {
           const int row = m0 + wm + mt * 16 + g + 8 * h;
           if (row >= M) continue;
 #pragma unroll
-          for (int nt = 0; nt < 4; nt++) {
+          for (int nt = 0; nt < NT; nt++) {
             const int col = n0 + wn + nt * 8 + 2 * t;
             if (col >= N) continue;
             const size_t at = (size_t)row * (size_t)N + (size_t)col;
@@ -433,44 +475,54 @@ static int default_dmma_shape() {
   return 2;
 }
 
-template <bool AK, bool BK_, int SHAPE, bool EDGE>
-static int launch_dmma_edge(const CUtensorMap &ma, const CUtensorMap &mb, const GemmEpilogue &ep,
-                            int M, int N, int K, int tiles_m, int tiles_n, int splits,
-                            int kt_per_split) {
+struct DmmaLaunch {
+  CUtensorMap ma, mb;
+  GemmEpilogue ep;
+  int M, N, K, tiles_m, tiles_n, splits, kt_per_split;
+};
+
+template <bool AK, bool BK_, int SHAPE, bool EDGE, class Cfg>
+static int launch_dmma_kernel(const DmmaLaunch &L) {
   static bool configured = false;
-  auto kernel = dmma_gemm_kernel<AK, BK_, SHAPE, EDGE>;
+  auto kernel = dmma_gemm_kernel<AK, BK_, SHAPE, EDGE, Cfg>;
   if (!configured) {
     MG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     kGemmSmemBytes));
+                                     Cfg::SMEM_BYTES));
     configured = true;
   }
   Context &c = ctx();
-  dim3 grid((unsigned)(tiles_m * tiles_n), 1, (unsigned)splits);
-  kernel<<<grid, kGemmThreads, kGemmSmemBytes, c.stream>>>(ma, mb, ep, M, N, K, tiles_n,
-                                                            kt_per_split, c.kernel_status);
+  dim3 grid((unsigned)(L.tiles_m * L.tiles_n), 1, (unsigned)L.splits);
+  kernel<<<grid, kGemmThreads, Cfg::SMEM_BYTES, c.stream>>>(L.ma, L.mb, L.ep, L.M, L.N, L.K,
+                                                             L.tiles_n, L.kt_per_split,
+                                                             c.kernel_status);
   MG_LAUNCH_CHECK("dmma_gemm");
   return MG_OK;
 }
 
+// Main configuration: every mma shape, with and without edge handling.
 template <bool AK, bool BK_, int SHAPE>
-static int launch_dmma(const CUtensorMap &ma, const CUtensorMap &mb, const GemmEpilogue &ep, int M,
-                       int N, int K, int tiles_m, int tiles_n, int splits, int kt_per_split) {
-  if ((M % BM) != 0 || (N % BN) != 0)
-    return launch_dmma_edge<AK, BK_, SHAPE, true>(ma, mb, ep, M, N, K, tiles_m, tiles_n, splits,
-                                                  kt_per_split);
-  return launch_dmma_edge<AK, BK_, SHAPE, false>(ma, mb, ep, M, N, K, tiles_m, tiles_n, splits,
-                                                 kt_per_split);
+static int launch_main(const DmmaLaunch &L) {
+  if ((L.M % MainCfg::BM) != 0 || (L.N % MainCfg::BN) != 0)
+    return launch_dmma_kernel<AK, BK_, SHAPE, true, MainCfg>(L);
+  return launch_dmma_kernel<AK, BK_, SHAPE, false, MainCfg>(L);
 }
 
+enum TileChoice { kTileMain = 0, kTileSkinny = 1, kTileHalf = 2 };
+
 template <bool AK, bool BK_>
-static int launch_dmma_shape(int shape, const CUtensorMap &ma, const CUtensorMap &mb,
-                             const GemmEpilogue &ep, int M, int N, int K, int tiles_m, int tiles_n,
-                             int splits, int kt_per_split) {
+static int launch_layout(int shape, int tile, const DmmaLaunch &L) {
+  // The narrow and half-width configurations exist for the default mma shape only.
+  if (tile == kTileSkinny) return launch_dmma_kernel<AK, BK_, 2, true, SkinnyCfg>(L);
+  if (tile == kTileHalf) {
+    if ((L.M % HalfCfg::BM) != 0 || (L.N % HalfCfg::BN) != 0)
+      return launch_dmma_kernel<AK, BK_, 2, true, HalfCfg>(L);
+    return launch_dmma_kernel<AK, BK_, 2, false, HalfCfg>(L);
+  }
   switch (shape) {
-    case 0: return launch_dmma<AK, BK_, 0>(ma, mb, ep, M, N, K, tiles_m, tiles_n, splits, kt_per_split);
-    case 1: return launch_dmma<AK, BK_, 1>(ma, mb, ep, M, N, K, tiles_m, tiles_n, splits, kt_per_split);
-    case 3: return launch_dmma<AK, BK_, 3>(ma, mb, ep, M, N, K, tiles_m, tiles_n, splits, kt_per_split);
-    default: return launch_dmma<AK, BK_, 2>(ma, mb, ep, M, N, K, tiles_m, tiles_n, splits, kt_per_split);
+    case 0: return launch_main<AK, BK_, 0>(L);
+    case 1: return launch_main<AK, BK_, 1>(L);
+    case 3: return launch_main<AK, BK_, 3>(L);
+    default: return launch_main<AK, BK_, 2>(L);
   }
 }
 
@@ -494,6 +546,43 @@ static int choose_splits(int tiles, int KT, int sms) {
     if (eff >= 0.95) return s;
   }
   return best;
+}
+
+// Tile configuration and contraction split for a problem.  Candidates are
+// costed as (waves of CTAs) x (work per CTA), with a small handicap for the
+// half-width tile (more operand traffic per flop) and for a split contraction
+// (its partial tiles are written and folded: ~22.8 (s+1)/K of the GEMM's time).
+struct GemmPlan {
+  int tile, bm, bn, splits;
+};
+
+static GemmPlan choose_plan(int M, int N, int K, int sms, int shape) {
+  const int KT = (K + BK - 1) / BK;
+  auto tiles_of = [&](int bm, int bn) { return ((M + bm - 1) / bm) * ((N + bn - 1) / bn); };
+  if (N <= SkinnyCfg::BN) {
+    return {kTileSkinny, SkinnyCfg::BM, SkinnyCfg::BN,
+            choose_splits(tiles_of(SkinnyCfg::BM, SkinnyCfg::BN), KT, sms)};
+  }
+  GemmPlan main_plan{kTileMain, MainCfg::BM, MainCfg::BN,
+                     choose_splits(tiles_of(MainCfg::BM, MainCfg::BN), KT, sms)};
+  static const int forced = [] {
+    const char *v = std::getenv("MG_GEMM_TILE");  // diagnostic: "main" or "half"
+    if (!v) return -1;
+    return v[0] == 'h' ? (int)kTileHalf : (v[0] == 'm' ? (int)kTileMain : -1);
+  }();
+  if (shape != 2 || forced == kTileMain) return main_plan;
+  GemmPlan half_plan{kTileHalf, HalfCfg::BM, HalfCfg::BN,
+                     choose_splits(tiles_of(HalfCfg::BM, HalfCfg::BN), KT, sms)};
+  if (forced == kTileHalf) return half_plan;
+  auto cost = [&](const GemmPlan &p, double handicap) {
+    const int ctas = tiles_of(p.bm, p.bn) * p.splits;
+    const int waves = (ctas + sms - 1) / sms;
+    const int kt = (KT + p.splits - 1) / p.splits;
+    double c = (double)waves * p.bm * p.bn * kt * handicap;
+    if (p.splits > 1) c *= 1.0 + 22.8 * (p.splits + 1) / (double)K;
+    return c;
+  };
+  return cost(half_plan, 1.04) < cost(main_plan, 1.0) ? half_plan : main_plan;
 }
 
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -546,16 +635,19 @@ static int run_gemm(const GemmDesc &d) {
     return MG_OK;
   }
 
-  CUtensorMap ma, mb;
-  bool ok_a = d.a_kcontig ? make_tensor_map_f64(&ma, d.A, d.M, d.K, BK, BM)
-                          : make_tensor_map_f64(&ma, d.A, d.K, d.M, 16, BK);
-  bool ok_b = d.b_kcontig ? make_tensor_map_f64(&mb, d.B, d.N, d.K, BK, BN)
-                          : make_tensor_map_f64(&mb, d.B, d.K, d.N, 16, BK);
+  const int shape = g_dmma_shape >= 0 ? g_dmma_shape : default_dmma_shape();
+  const GemmPlan plan = choose_plan(M, N, K, c.sm_count, shape);
+  const int bm = plan.bm, bn = plan.bn;
+  DmmaLaunch L;
+  bool ok_a = d.a_kcontig ? make_tensor_map_f64(&L.ma, d.A, d.M, d.K, BK, bm)
+                          : make_tensor_map_f64(&L.ma, d.A, d.K, d.M, 16, BK);
+  bool ok_b = d.b_kcontig ? make_tensor_map_f64(&L.mb, d.B, d.N, d.K, BK, bn)
+                          : make_tensor_map_f64(&L.mb, d.B, d.K, d.N, 16, BK);
   if (!ok_a || !ok_b) return fail(MG_ERR_CUDA, "gemm: cuTensorMapEncodeTiled failed");
 
-  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int tiles_m = (M + bm - 1) / bm, tiles_n = (N + bn - 1) / bn;
   const int KT = (K + BK - 1) / BK;
-  int splits = choose_splits(tiles_m * tiles_n, KT, c.sm_count);
+  int splits = plan.splits;
   int kt_per_split = (KT + splits - 1) / splits;
   splits = (KT + kt_per_split - 1) / kt_per_split;
   if (splits > 1) {
@@ -564,14 +656,16 @@ static int run_gemm(const GemmDesc &d) {
     if (rc != MG_OK) return rc;
     ep.partial = c.splitk_scratch;
   }
-  const int shape = g_dmma_shape >= 0 ? g_dmma_shape : default_dmma_shape();
+  L.ep = ep;
+  L.M = M; L.N = N; L.K = K;
+  L.tiles_m = tiles_m; L.tiles_n = tiles_n; L.splits = splits; L.kt_per_split = kt_per_split;
   int rc;
   if (d.a_kcontig && !d.b_kcontig)
-    rc = launch_dmma_shape<true, false>(shape, ma, mb, ep, M, N, K, tiles_m, tiles_n, splits, kt_per_split);
+    rc = launch_layout<true, false>(shape, plan.tile, L);
   else if (d.a_kcontig && d.b_kcontig)
-    rc = launch_dmma_shape<true, true>(shape, ma, mb, ep, M, N, K, tiles_m, tiles_n, splits, kt_per_split);
+    rc = launch_layout<true, true>(shape, plan.tile, L);
   else if (!d.a_kcontig && !d.b_kcontig)
-    rc = launch_dmma_shape<false, false>(shape, ma, mb, ep, M, N, K, tiles_m, tiles_n, splits, kt_per_split);
+    rc = launch_layout<false, false>(shape, plan.tile, L);
   else
     return fail(MG_ERR_INVALID, "gemm: unsupported operand layout");
   if (rc != MG_OK) return rc;
