@@ -67,6 +67,15 @@ int mg_alloc_i32(size_t n, int **out);
 int mg_free_i32(int *p);
 int mg_upload(double *dst, const double *src_host, size_t n);   /* pageable or pinned host */
 int mg_download(double *dst_host, const double *src, size_t n); /* blocks until done */
+/* Prefetch: copies on a separate copy stream, so the transfer of the next batch
+ * overlaps kernels already enqueued on the compute stream.  The copy starts once
+ * the compute stream has reached the point of this call (dst is then safe to
+ * write) and *out_event_id completes when the data has landed.  Before the first
+ * kernel that reads dst, call mg_compute_wait_event(id), then mg_event_destroy(id).
+ * src_host must stay unchanged until the event completes (pinned memory makes the
+ * copy asynchronous to the host). */
+int mg_upload_async(double *dst, const double *src_host, size_t n, int *out_event_id);
+int mg_compute_wait_event(int id); /* compute stream waits for the event, not the host */
 int mg_upload_i32(int *dst, const int *src_host, size_t n);
 int mg_download_i32(int *dst_host, const int *src, size_t n);
 int mg_fill(double *dst, double value, size_t n); /* Tensor.cpp:12-13, 73-77; Autograd.cpp:23-25 */

@@ -108,4 +108,12 @@ private:
   std::string op_;
   micrograd::Backend backend_ = micrograd::Backend::CPU;
   bool requires_grad_ = true;
+
+  // Set on the output of a fused linear+ReLU node.  A consumer that writes this
+  // node's gradient with a GEMM applies the ReLU mask in that GEMM's epilogue
+  // and records the gradient's write stamp; if nothing else has written the
+  // gradient since, the node's own backward skips its mask pass.
+  bool relu_output_ = false;
+  bool grad_premasked_ = false;
+  unsigned long long grad_premasked_stamp_ = 0;
 };

@@ -25,7 +25,10 @@ public:
   void init_zero(size_t n);
   // Takes ownership of host values and uploads them.
   void init_from_host(std::vector<double> &&values);
-  // Uploads `n` values straight from caller memory (may be pinned).
+  // Uploads `n` values straight from caller memory (may be pinned) on the copy
+  // stream, so the transfer overlaps kernels already enqueued; the first kernel
+  // that touches the buffer waits for it on the device.  The caller keeps
+  // `values` unchanged until then.
   void init_from_pointer(const double *values, size_t n);
 
   size_t size() const { return size_; }
@@ -56,9 +59,13 @@ public:
   // True when the device buffer holds the current values (not logical zeros,
   // not superseded by a lent host view).
   bool device_current() const { return !zero_ && dev_valid_; }
+  // Counts every hand-out of the contents for writing (device or host); lets a
+  // caller detect that nobody has touched the buffer since it last looked.
+  unsigned long long write_stamp() const { return write_stamp_; }
 
 private:
   void ensure_device_buffer();
+  void settle_upload();  // make the compute stream wait for a pending prefetch
   void sync_device_from_host();
   void sync_host_from_device();
 
@@ -69,6 +76,8 @@ private:
   bool zero_ = true;         // logically all zeros; dev_/host_ contents irrelevant
   bool dev_valid_ = false;   // dev_ holds the current values
   bool host_valid_ = false;  // host_ holds the current values
+  unsigned long long write_stamp_ = 0;
+  int pending_upload_ = -1;  // event id of a prefetch the compute stream has not waited for
   std::vector<double> host_;
 };
 

@@ -23,6 +23,9 @@ public:
   std::shared_ptr<Tensor> bias();
 
   // addition: relu(forward(input)) as a single node (bias + ReLU epilogue).
+  // When the node feeding gradient into it is another Linear, that layer's dX
+  // GEMM applies this node's ReLU mask in its epilogue; grad() of the returned
+  // tensor then holds the gradient with respect to the pre-activation.
   std::shared_ptr<Tensor> forward_relu(const std::shared_ptr<Tensor> &input);
 
 private:

@@ -42,6 +42,8 @@ SIGNATURES = {
     "mg_free_i32": (C.c_int, [C.c_void_p]),
     "mg_upload": (C.c_int, [C.c_void_p, C.c_void_p, _sz]),
     "mg_download": (C.c_int, [C.c_void_p, C.c_void_p, _sz]),
+    "mg_upload_async": (C.c_int, [C.c_void_p, C.c_void_p, _sz, _ip]),
+    "mg_compute_wait_event": (C.c_int, [C.c_int]),
     "mg_upload_i32": (C.c_int, [C.c_void_p, C.c_void_p, _sz]),
     "mg_download_i32": (C.c_int, [C.c_void_p, C.c_void_p, _sz]),
     "mg_fill": (C.c_int, [C.c_void_p, C.c_double, _sz]),

@@ -24,6 +24,8 @@ struct Context {
   int sm_count = 0;
   cudaStream_t stream = nullptr;       // compute stream (ordered)
   cudaStream_t comm_stream = nullptr;  // NCCL all-reduces
+  cudaStream_t copy_stream = nullptr;  // host -> device prefetch of the next batch
+  cudaEvent_t copy_fork_event = nullptr;  // compute -> copy ordering (buffer is allocated)
   cudaEvent_t fork_event = nullptr;    // compute -> comm ordering
   cudaEvent_t join_event = nullptr;    // comm -> compute ordering
   // Scratch for reductions: partial sums and the "blocks done" ticket.

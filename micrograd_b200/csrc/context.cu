@@ -74,6 +74,8 @@ static int init_locked(int device) {
   int prio_least = 0, prio_greatest = 0;
   MG_CUDA_TRY(cudaDeviceGetStreamPriorityRange(&prio_least, &prio_greatest));
   MG_CUDA_TRY(cudaStreamCreateWithPriority(&c.comm_stream, cudaStreamNonBlocking, prio_greatest));
+  MG_CUDA_TRY(cudaStreamCreateWithFlags(&c.copy_stream, cudaStreamNonBlocking));
+  MG_CUDA_TRY(cudaEventCreateWithFlags(&c.copy_fork_event, cudaEventDisableTiming));
   MG_CUDA_TRY(cudaEventCreateWithFlags(&c.fork_event, cudaEventDisableTiming));
   MG_CUDA_TRY(cudaEventCreateWithFlags(&c.join_event, cudaEventDisableTiming));
   // Keep freed blocks in the stream-ordered pool instead of returning them to
@@ -137,6 +139,8 @@ int mg_shutdown(void) {
   cudaFree(c.reduce_ticket);
   cudaFree(c.kernel_status);
   if (c.flush_buf) cudaFree(c.flush_buf);
+  cudaEventDestroy(c.copy_fork_event);
+  cudaStreamDestroy(c.copy_stream);
   cudaEventDestroy(c.fork_event);
   cudaEventDestroy(c.join_event);
   cudaStreamDestroy(c.stream);
@@ -158,6 +162,7 @@ int mg_sync(void) {
   MG_ENSURE_INIT();
   MG_CUDA_TRY(cudaStreamSynchronize(g_ctx.stream));
   MG_CUDA_TRY(cudaStreamSynchronize(g_ctx.comm_stream));
+  MG_CUDA_TRY(cudaStreamSynchronize(g_ctx.copy_stream));
   return MG_OK;
 }
 
@@ -216,6 +221,34 @@ int mg_upload(double *dst, const double *src_host, size_t n) {
   if (!dst || !src_host) return fail(MG_ERR_INVALID, "mg_upload: null pointer");
   MG_CUDA_TRY(cudaMemcpyAsync(dst, src_host, n * sizeof(double), cudaMemcpyHostToDevice,
                               g_ctx.stream));
+  return MG_OK;
+}
+
+int mg_upload_async(double *dst, const double *src_host, size_t n, int *out_event_id) {
+  MG_ENSURE_INIT();
+  if (!out_event_id) return fail(MG_ERR_INVALID, "mg_upload_async: null event pointer");
+  if (n && (!dst || !src_host)) return fail(MG_ERR_INVALID, "mg_upload_async: null pointer");
+  Context &c = g_ctx;
+  // dst comes from the stream-ordered pool on the compute stream: the copy may
+  // touch it only once the compute stream has passed the point of allocation.
+  MG_CUDA_TRY(cudaEventRecord(c.copy_fork_event, c.stream));
+  MG_CUDA_TRY(cudaStreamWaitEvent(c.copy_stream, c.copy_fork_event, 0));
+  if (n)
+    MG_CUDA_TRY(cudaMemcpyAsync(dst, src_host, n * sizeof(double), cudaMemcpyHostToDevice,
+                                c.copy_stream));
+  int id = -1;
+  int rc = mg_event_create(&id);
+  if (rc != MG_OK) return rc;
+  MG_CUDA_TRY(cudaEventRecord(g_events[id], c.copy_stream));
+  *out_event_id = id;
+  return MG_OK;
+}
+
+int mg_compute_wait_event(int id) {
+  MG_ENSURE_INIT();
+  if (id < 0 || (size_t)id >= g_events.size() || !g_events[id])
+    return fail(MG_ERR_INVALID, "unknown event id %d", id);
+  MG_CUDA_TRY(cudaStreamWaitEvent(g_ctx.stream, g_events[id], 0));
   return MG_OK;
 }
 

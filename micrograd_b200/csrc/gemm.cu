@@ -17,7 +17,7 @@
 //     accumulates 16 bytes per thread per row.
 //   - When the output has too few tiles to fill 148 SMs (weight gradients: the
 //     contraction runs over the batch), the contraction is split across
-//     gridDim.z and a second kernel folds the partial tiles in index order, so
+//     the grid and a second kernel folds the partial tiles in index order, so
 //     the result is still reproducible.
 // Fallback kernel: a plain shared-memory tiled FMA kernel with full bounds
 // checks for shapes the TMA path cannot take (odd row lengths, unaligned
@@ -216,13 +216,13 @@ __device__ __forceinline__ bool consumer_loop(double (&acc)[Cfg::MT][Cfg::NT][4]
 }
 
 // SHAPE: 0 m8n8k4, 1 m16n8k4, 2 m16n8k8, 3 m16n8k16.
-// EDGE: the problem has ragged tiles (M or N not a multiple of 128); only then is
-// the per-sub-tile skipping compiled in, so the interior-only kernel stays lean.
+// EDGE: the problem has ragged tiles (M or N not a multiple of the tile); only
+// then is the per-sub-tile skipping compiled in.
 template <bool A_KCONTIG, bool B_KCONTIG, int SHAPE, bool EDGE, class Cfg>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-                 GemmEpilogue ep, int M, int N, int K, int tiles_n, int kt_per_split,
-                 int *status) {
+                 GemmEpilogue ep, int M, int N, int K, int tiles_n, int heavy_tiles, int light_tiles,
+                 int splits, int kt_per_split, int *status) {
   constexpr int BM = Cfg::BM, BN = Cfg::BN, MT = Cfg::MT, NT = Cfg::NT;
   constexpr int kStages = Cfg::STAGES, kStageBytes = Cfg::STAGE_BYTES, kTileBytes = Cfg::A_BYTES;
   extern __shared__ uint8_t smem_raw[];
@@ -235,10 +235,29 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
   uint64_t *empty_bar = full_bar + kStages;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile_m = blockIdx.x / tiles_n, tile_n = blockIdx.x % tiles_n;
+  // Work order.  Tiles are numbered row-major; the first `heavy_tiles` of them are
+  // (at least half) full, the remaining `light_tiles` are the thin bottom border
+  // of a ragged problem.  CTAs are issued split by split over the heavy tiles
+  // (CTAs of one wave then share the same k-range of both operands in L2), and
+  // all light tiles come last, so that short CTAs fill the tail of the last
+  // wave instead of pushing full ones into an extra wave.
+  int tile, split;
+  {
+    const int id = blockIdx.x;
+    const int heavy_ctas = heavy_tiles * splits;
+    if (id < heavy_ctas) {
+      split = id / heavy_tiles;
+      tile = id - split * heavy_tiles;
+    } else {
+      const int j = id - heavy_ctas;
+      split = j / light_tiles;
+      tile = heavy_tiles + (j - split * light_tiles);
+    }
+  }
+  const int tile_m = tile / tiles_n, tile_n = tile - tile_m * tiles_n;
   const int m0 = tile_m * BM, n0 = tile_n * BN;
   const int KT = (K + BK - 1) / BK;
-  const int kt_begin = blockIdx.z * kt_per_split;
+  const int kt_begin = split * kt_per_split;
   const int kt_end = min(KT, kt_begin + kt_per_split);
   const int nkt = kt_end - kt_begin;
 
@@ -324,7 +343,7 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
 
     if (ok) {
       // ---------------- epilogue ----------------
-      double *dst = ep.partial ? ep.partial + (size_t)blockIdx.z * (size_t)M * (size_t)N : ep.D;
+      double *dst = ep.partial ? ep.partial + (size_t)split * (size_t)M * (size_t)N : ep.D;
 #pragma unroll
       for (int mt = 0; mt < MT; mt++) {
 #pragma unroll
@@ -481,8 +500,14 @@ struct DmmaLaunch {
   int M, N, K, tiles_m, tiles_n, splits, kt_per_split;
 };
 
+// A rectangle of tiles: rows [m0, m0 + rows), columns [n0, n0 + cols).
+struct TileRegion {
+  int m0, n0, rows, cols;
+};
+
 template <bool AK, bool BK_, int SHAPE, bool EDGE, class Cfg>
-static int launch_dmma_kernel(const DmmaLaunch &L) {
+static int launch_dmma_kernel(const DmmaLaunch &L, const TileRegion &R) {
+  if (R.rows <= 0 || R.cols <= 0) return MG_OK;
   static bool configured = false;
   auto kernel = dmma_gemm_kernel<AK, BK_, SHAPE, EDGE, Cfg>;
   if (!configured) {
@@ -491,20 +516,25 @@ static int launch_dmma_kernel(const DmmaLaunch &L) {
     configured = true;
   }
   Context &c = ctx();
-  dim3 grid((unsigned)(L.tiles_m * L.tiles_n), 1, (unsigned)L.splits);
-  kernel<<<grid, kGemmThreads, Cfg::SMEM_BYTES, c.stream>>>(L.ma, L.mb, L.ep, L.M, L.N, L.K,
-                                                             L.tiles_n, L.kt_per_split,
+  const int tiles = R.rows * R.cols;
+  // bottom row of tiles less than half full -> its tiles are "light"
+  const int light = ((L.M % Cfg::BM) != 0 && (L.M % Cfg::BM) * 2 < Cfg::BM && R.rows > 1) ? R.cols : 0;
+  dim3 grid((unsigned)(tiles * L.splits), 1, 1);
+  kernel<<<grid, kGemmThreads, Cfg::SMEM_BYTES, c.stream>>>(L.ma, L.mb, L.ep, L.M, L.N, L.K, R.cols,
+                                                             tiles - light, light, L.splits, L.kt_per_split,
                                                              c.kernel_status);
   MG_LAUNCH_CHECK("dmma_gemm");
   return MG_OK;
 }
 
-// Main configuration: every mma shape, with and without edge handling.
-template <bool AK, bool BK_, int SHAPE>
-static int launch_main(const DmmaLaunch &L) {
-  if ((L.M % MainCfg::BM) != 0 || (L.N % MainCfg::BN) != 0)
-    return launch_dmma_kernel<AK, BK_, SHAPE, true, MainCfg>(L);
-  return launch_dmma_kernel<AK, BK_, SHAPE, false, MainCfg>(L);
+// One launch over all tiles; problems with a ragged border use the instantiation
+// that can skip out-of-range sub-tiles.
+template <bool AK, bool BK_, int SHAPE, class Cfg>
+static int launch_regions(const DmmaLaunch &L) {
+  const TileRegion all{0, 0, L.tiles_m, L.tiles_n};
+  if ((L.M % Cfg::BM) != 0 || (L.N % Cfg::BN) != 0)
+    return launch_dmma_kernel<AK, BK_, SHAPE, true, Cfg>(L, all);
+  return launch_dmma_kernel<AK, BK_, SHAPE, false, Cfg>(L, all);
 }
 
 enum TileChoice { kTileMain = 0, kTileSkinny = 1, kTileHalf = 2 };
@@ -512,17 +542,14 @@ enum TileChoice { kTileMain = 0, kTileSkinny = 1, kTileHalf = 2 };
 template <bool AK, bool BK_>
 static int launch_layout(int shape, int tile, const DmmaLaunch &L) {
   // The narrow and half-width configurations exist for the default mma shape only.
-  if (tile == kTileSkinny) return launch_dmma_kernel<AK, BK_, 2, true, SkinnyCfg>(L);
-  if (tile == kTileHalf) {
-    if ((L.M % HalfCfg::BM) != 0 || (L.N % HalfCfg::BN) != 0)
-      return launch_dmma_kernel<AK, BK_, 2, true, HalfCfg>(L);
-    return launch_dmma_kernel<AK, BK_, 2, false, HalfCfg>(L);
-  }
+  if (tile == kTileSkinny)
+    return launch_dmma_kernel<AK, BK_, 2, true, SkinnyCfg>(L, TileRegion{0, 0, L.tiles_m, L.tiles_n});
+  if (tile == kTileHalf) return launch_regions<AK, BK_, 2, HalfCfg>(L);
   switch (shape) {
-    case 0: return launch_main<AK, BK_, 0>(L);
-    case 1: return launch_main<AK, BK_, 1>(L);
-    case 3: return launch_main<AK, BK_, 3>(L);
-    default: return launch_main<AK, BK_, 2>(L);
+    case 0: return launch_regions<AK, BK_, 0, MainCfg>(L);
+    case 1: return launch_regions<AK, BK_, 1, MainCfg>(L);
+    case 3: return launch_regions<AK, BK_, 3, MainCfg>(L);
+    default: return launch_regions<AK, BK_, 2, MainCfg>(L);
   }
 }
 
@@ -558,7 +585,13 @@ struct GemmPlan {
 
 static GemmPlan choose_plan(int M, int N, int K, int sms, int shape) {
   const int KT = (K + BK - 1) / BK;
-  auto tiles_of = [&](int bm, int bn) { return ((M + bm - 1) / bm) * ((N + bn - 1) / bn); };
+  // Tiles that are at least half full decide how the waves fill up; the thin
+  // border tiles of a ragged problem are short and slot into the gaps.
+  auto tiles_of = [&](int bm, int bn) {
+    const int tm = (M % bm) * 2 >= bm ? (M + bm - 1) / bm : M / bm;
+    const int tn = (N % bn) * 2 >= bn ? (N + bn - 1) / bn : N / bn;
+    return (tm > 0 ? tm : 1) * (tn > 0 ? tn : 1);
+  };
   if (N <= SkinnyCfg::BN) {
     return {kTileSkinny, SkinnyCfg::BM, SkinnyCfg::BN,
             choose_splits(tiles_of(SkinnyCfg::BM, SkinnyCfg::BN), KT, sms)};

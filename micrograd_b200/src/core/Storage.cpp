@@ -15,6 +15,11 @@ void check(int rc, const char *what) {
 }
 
 Storage::~Storage() {
+  if (pending_upload_ >= 0) {
+    // never read: still order the free after the copy
+    mg_compute_wait_event(pending_upload_);
+    mg_event_destroy(pending_upload_);
+  }
   if (dev_ && owns_dev_) {
     mg_free(dev_);
   }
@@ -45,10 +50,18 @@ void Storage::init_from_host(std::vector<double> &&values) {
   host_valid_ = false;
 }
 
+void Storage::settle_upload() {
+  if (pending_upload_ >= 0) {
+    check(mg_compute_wait_event(pending_upload_), "wait for upload");
+    check(mg_event_destroy(pending_upload_), "event destroy");
+    pending_upload_ = -1;
+  }
+}
+
 void Storage::init_from_pointer(const double *values, size_t n) {
   size_ = n;
   ensure_device_buffer();
-  check(mg_upload(dev_, values, n), "upload");
+  check(mg_upload_async(dev_, values, n, &pending_upload_), "upload");
   zero_ = false;
   dev_valid_ = true;
   host_valid_ = false;
@@ -67,6 +80,7 @@ void Storage::sync_host_from_device() {
 }
 
 const double *Storage::device_read() {
+  settle_upload();
   if (zero_) {
     ensure_device_buffer();
     check(mg_fill(dev_, 0.0, size_), "fill");
@@ -80,6 +94,8 @@ const double *Storage::device_read() {
 }
 
 double *Storage::device_overwrite() {
+  write_stamp_++;
+  settle_upload();
   ensure_device_buffer();
   zero_ = false;
   dev_valid_ = true;
@@ -88,6 +104,8 @@ double *Storage::device_overwrite() {
 }
 
 double *Storage::device_accumulate(bool *store) {
+  write_stamp_++;
+  settle_upload();
   if (zero_) {
     ensure_device_buffer();
     *store = true;
@@ -105,18 +123,23 @@ double *Storage::device_accumulate(bool *store) {
 }
 
 double *Storage::device_update() {
+  write_stamp_++;
   device_read();
   host_valid_ = false;
   return dev_;
 }
 
 void Storage::set_zero() {
+  write_stamp_++;
+  settle_upload();
   zero_ = true;
   dev_valid_ = false;
   host_valid_ = false;
 }
 
 void Storage::fill(double value) {
+  write_stamp_++;
+  settle_upload();
   ensure_device_buffer();
   check(mg_fill(dev_, value, size_), "fill");
   zero_ = false;
@@ -125,6 +148,7 @@ void Storage::fill(double value) {
 }
 
 std::vector<double> &Storage::host_mutable() {
+  write_stamp_++;
   host_const();
   // The caller may write through the reference at any later time, so the host
   // vector is the authority until a kernel needs the values again.
@@ -133,6 +157,7 @@ std::vector<double> &Storage::host_mutable() {
 }
 
 const std::vector<double> &Storage::host_const() {
+  settle_upload();
   if (zero_) {
     host_.assign(size_, 0.0);
     zero_ = false;
@@ -145,6 +170,7 @@ const std::vector<double> &Storage::host_const() {
 }
 
 double Storage::peek(size_t index) {
+  settle_upload();
   if (zero_ || index >= size_) {
     return 0.0;
   }
@@ -157,6 +183,7 @@ double Storage::peek(size_t index) {
 }
 
 void Storage::rehome(double *slice, std::shared_ptr<void> keepalive) {
+  settle_upload();
   if (!zero_) {
     if (dev_valid_) {
       check(mg_copy(slice, dev_, size_), "copy");

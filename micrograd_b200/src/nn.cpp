@@ -24,6 +24,18 @@ struct TensorAccess {
   static std::function<void(Tensor &)> &backward_fn(Tensor &t) { return t.backward_fn_; }
   static std::function<void(Tensor &)> &hook(Tensor &t) { return t.grad_ready_hook_; }
   static bool requires_grad(const Tensor &t) { return t.requires_grad_; }
+  static void mark_relu_output(Tensor &t) { t.relu_output_ = true; }
+  static bool is_relu_output(const Tensor &t) { return t.relu_output_; }
+  // True if the gradient buffer holds only values that already carry the ReLU
+  // mask (or nothing at all).
+  static bool grad_fully_masked(Tensor &t) {
+    return t.grad_.is_zero() || (t.grad_premasked_ && t.grad_.device_current() &&
+                                 t.grad_.write_stamp() == t.grad_premasked_stamp_);
+  }
+  static void commit_premask(Tensor &t, bool fully_masked) {
+    t.grad_premasked_ = fully_masked;
+    t.grad_premasked_stamp_ = t.grad_.write_stamp();
+  }
   static std::shared_ptr<Tensor> make_result(Tensor &owner, std::vector<size_t> shape,
                                              std::string label,
                                              std::vector<std::shared_ptr<Tensor>> children) {
@@ -105,6 +117,10 @@ std::shared_ptr<Tensor> Linear::fused_forward(const std::shared_ptr<Tensor> &inp
                    relu ? MG_EPI_BIAS_RELU : MG_EPI_BIAS, Access::data(*bias_).device_read()),
         "linear forward");
 
+  if (relu) {
+    Access::mark_relu_output(*result);
+  }
+
   Access::backward_fn(*result) = [batch, in, out, relu](Tensor &self) {
     if (Access::grad(self).is_zero()) {
       return;
@@ -113,9 +129,12 @@ std::shared_ptr<Tensor> Linear::fused_forward(const std::shared_ptr<Tensor> &inp
     Tensor &x = *kids[0];
     Tensor &w = *kids[1];
     Tensor &b = *kids[2];
+    // An upstream GEMM may already have applied this node's ReLU mask while
+    // writing the gradient (see the dX product below).
+    const bool premasked = relu && !Access::grad(self).is_zero() && Access::grad_fully_masked(self);
     const double *g = Access::grad(self).device_read();
     double *masked = nullptr;
-    if (relu) {
+    if (relu && !premasked) {
       // dZ = dOut * (out > 0); out > 0 exactly where the pre-activation was.
       check(mg_alloc(batch * out, &masked), "device allocation");
       check(mg_unary_bwd(MG_RELU, Access::data(self).device_read(), nullptr, 0.0, g, masked,
@@ -134,10 +153,19 @@ std::shared_ptr<Tensor> Linear::fused_forward(const std::shared_ptr<Tensor> &inp
       check(mg_add_row_bwd(g, nullptr, gb, batch, out, store ? MG_ACC_STORE_B : 0), "linear db");
     }
     if (Access::requires_grad(x)) {
+      // If the input is itself the output of a linear+ReLU node, its backward
+      // would multiply this gradient by (x > 0) in a separate pass over the
+      // whole activation; the GEMM epilogue does it for free.
+      const bool mask_input = Access::is_relu_output(x);
+      const bool stays_masked = mask_input && Access::grad_fully_masked(x);
       double *gx = Access::grad(x).device_accumulate(&store);
       check(mg_gemm_nt(g, Access::data(w).device_read(), gx, batch, out, in, store ? 0 : 1,
-                       MG_EPI_NONE, nullptr),
+                       mask_input ? MG_EPI_RELU_MASK : MG_EPI_NONE,
+                       mask_input ? Access::data(x).device_read() : nullptr),
             "linear dX");
+      if (mask_input) {
+        Access::commit_premask(x, stays_masked);
+      }
     }
     if (masked) {
       check(mg_free(masked), "free");
