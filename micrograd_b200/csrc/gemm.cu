@@ -92,13 +92,12 @@ __device__ __forceinline__ double2 apply_epilogue(double2 v, const GemmEpilogue 
 
 // Fragment pair (k = 2c, 2c+1) of the A operand for the MT row sub-tiles of a
 // warp: lo = rows g, hi = rows g + 8 of each 16-row sub-tile.
-template <bool KCONTIG, bool FULL, int MT>
-__device__ __forceinline__ void load_a_frags(const uint8_t *As, int c, int g, int wm, int mt_count,
+template <bool KCONTIG, int MT>
+__device__ __forceinline__ void load_a_frags(const uint8_t *As, int c, int g, int wm,
                                              double2 (&lo)[MT], double2 (&hi)[MT]) {
   if (KCONTIG) {
 #pragma unroll
     for (int mt = 0; mt < MT; mt++) {
-      if (!FULL && mt >= mt_count) continue;
       const int off = (wm + mt * 16 + g) * 128 + ((c ^ g) << 4);
       lo[mt] = *reinterpret_cast<const double2 *>(As + off);
       hi[mt] = *reinterpret_cast<const double2 *>(As + off + 8 * 128);
@@ -107,7 +106,6 @@ __device__ __forceinline__ void load_a_frags(const uint8_t *As, int c, int g, in
     const int ka = 2 * c, kb = 2 * c + 1;
 #pragma unroll
     for (int mt = 0; mt < MT; mt++) {
-      if (!FULL && mt >= mt_count) continue;
       const int base = ((wm >> 4) + mt) * 2048;
       const int mlo = g, mhi = g + 8;
       lo[mt].x = *reinterpret_cast<const double *>(
@@ -123,13 +121,12 @@ __device__ __forceinline__ void load_a_frags(const uint8_t *As, int c, int g, in
 }
 
 // Fragment pair of the B operand for the NT column sub-tiles of a warp (column g).
-template <bool KCONTIG, bool FULL, int NT>
-__device__ __forceinline__ void load_b_frags(const uint8_t *Bs, int c, int g, int wn, int nt_count,
+template <bool KCONTIG, int NT>
+__device__ __forceinline__ void load_b_frags(const uint8_t *Bs, int c, int g, int wn,
                                              double2 (&b)[NT]) {
   if (KCONTIG) {
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
-      if (!FULL && nt >= nt_count) continue;
       const int off = (wn + nt * 8 + g) * 128 + ((c ^ g) << 4);
       b[nt] = *reinterpret_cast<const double2 *>(Bs + off);
     }
@@ -137,7 +134,6 @@ __device__ __forceinline__ void load_b_frags(const uint8_t *Bs, int c, int g, in
     const int ka = 2 * c, kb = 2 * c + 1;
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
-      if (!FULL && nt >= nt_count) continue;
       const int nl = wn + nt * 8 + g;
       const int base = (nl >> 4) * 2048, nn = nl & 15;
       b[nt].x = *reinterpret_cast<const double *>(
@@ -148,22 +144,20 @@ __device__ __forceinline__ void load_b_frags(const uint8_t *Bs, int c, int g, in
   }
 }
 
-// One 16-deep stage of MMAs for a warp.  FULL: every sub-tile is live.
-template <bool A_KCONTIG, bool B_KCONTIG, int SHAPE, bool FULL, int MT, int NT>
+// One 16-deep stage of MMAs for a warp.
+template <bool A_KCONTIG, bool B_KCONTIG, int SHAPE, int MT, int NT>
 __device__ __forceinline__ void compute_stage(double (&acc)[MT][NT][4], const uint8_t *As,
-                                              const uint8_t *Bs, int c0, int g, int wm, int wn,
-                                              int mt_count, int nt_count) {
+                                              const uint8_t *Bs, int c0, int g, int wm, int wn) {
   if (SHAPE == 3) {
     double2 lo0[MT], hi0[MT], b0[NT], lo1[MT], hi1[MT], b1[NT];
-    load_a_frags<A_KCONTIG, FULL, MT>(As, c0, g, wm, mt_count, lo0, hi0);
-    load_b_frags<B_KCONTIG, FULL, NT>(Bs, c0, g, wn, nt_count, b0);
-    load_a_frags<A_KCONTIG, FULL, MT>(As, c0 ^ 1, g, wm, mt_count, lo1, hi1);
-    load_b_frags<B_KCONTIG, FULL, NT>(Bs, c0 ^ 1, g, wn, nt_count, b1);
+    load_a_frags<A_KCONTIG, MT>(As, c0, g, wm, lo0, hi0);
+    load_b_frags<B_KCONTIG, NT>(Bs, c0, g, wn, b0);
+    load_a_frags<A_KCONTIG, MT>(As, c0 ^ 1, g, wm, lo1, hi1);
+    load_b_frags<B_KCONTIG, NT>(Bs, c0 ^ 1, g, wn, b1);
 #pragma unroll
     for (int mt = 0; mt < MT; mt++)
 #pragma unroll
       for (int nt = 0; nt < NT; nt++) {
-        if (!FULL && (mt >= mt_count || nt >= nt_count)) continue;
         dmma_m16n8k16(acc[mt][nt], lo0[mt].x, hi0[mt].x, lo0[mt].y, hi0[mt].y, lo1[mt].x, hi1[mt].x,
                       lo1[mt].y, hi1[mt].y, b0[nt].x, b0[nt].y, b1[nt].x, b1[nt].y);
       }
@@ -171,14 +165,13 @@ __device__ __forceinline__ void compute_stage(double (&acc)[MT][NT][4], const ui
 #pragma unroll
     for (int slab = 0; slab < 2; slab++) {
       double2 lo[MT], hi[MT], b[NT];
-      load_a_frags<A_KCONTIG, FULL, MT>(As, c0 ^ slab, g, wm, mt_count, lo, hi);
-      load_b_frags<B_KCONTIG, FULL, NT>(Bs, c0 ^ slab, g, wn, nt_count, b);
+      load_a_frags<A_KCONTIG, MT>(As, c0 ^ slab, g, wm, lo, hi);
+      load_b_frags<B_KCONTIG, NT>(Bs, c0 ^ slab, g, wn, b);
 #pragma unroll
       for (int mt = 0; mt < MT; mt++)
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
-          if (!FULL && (mt >= mt_count || nt >= nt_count)) continue;
-          if (SHAPE == 2) {
+            if (SHAPE == 2) {
             dmma_m16n8k8(acc[mt][nt], lo[mt].x, hi[mt].x, lo[mt].y, hi[mt].y, b[nt].x, b[nt].y);
           } else if (SHAPE == 1) {
             dmma_m16n8k4(acc[mt][nt], lo[mt].x, hi[mt].x, b[nt].x);
@@ -195,20 +188,21 @@ __device__ __forceinline__ void compute_stage(double (&acc)[MT][NT][4], const ui
 }
 
 // Consumer side of the stage ring: wait for a stage, run its MMAs, hand the
-// stage back.  Returns false if a bounded wait gave up.
-template <bool A_KCONTIG, bool B_KCONTIG, int SHAPE, bool FULL, class Cfg>
+// stage back.  `active` is false for a warp whose whole sub-block lies outside
+// the matrix (ragged border tiles): it skips the arithmetic but keeps the
+// barrier protocol.  Returns false if a bounded wait gave up.
+template <bool A_KCONTIG, bool B_KCONTIG, int SHAPE, class Cfg>
 __device__ __forceinline__ bool consumer_loop(double (&acc)[Cfg::MT][Cfg::NT][4], const uint8_t *smem,
                                               uint64_t *full_bar, uint64_t *empty_bar, int nkt,
                                               volatile int *abort_flag, int c0, int g, int wm, int wn,
-                                              int lane, int mt_count, int nt_count) {
+                                              int lane, bool active) {
   for (int it = 0; it < nkt; ++it) {
     const int s = it % Cfg::STAGES;
     if (!mbar_wait_bounded(smem_u32(full_bar + s), (it / Cfg::STAGES) & 1, abort_flag)) return false;
     const uint8_t *As = smem + s * Cfg::STAGE_BYTES;
     const uint8_t *Bs = As + Cfg::A_BYTES;
-    if (FULL || (mt_count > 0 && nt_count > 0))
-      compute_stage<A_KCONTIG, B_KCONTIG, SHAPE, FULL, Cfg::MT, Cfg::NT>(acc, As, Bs, c0, g, wm, wn,
-                                                                         mt_count, nt_count);
+    if (active)
+      compute_stage<A_KCONTIG, B_KCONTIG, SHAPE, Cfg::MT, Cfg::NT>(acc, As, Bs, c0, g, wm, wn);
     __syncwarp();
     if (lane == 0) mbar_arrive(smem_u32(empty_bar + s));
   }
@@ -217,12 +211,12 @@ __device__ __forceinline__ bool consumer_loop(double (&acc)[Cfg::MT][Cfg::NT][4]
 
 // SHAPE: 0 m8n8k4, 1 m16n8k4, 2 m16n8k8, 3 m16n8k16.
 // EDGE: the problem has ragged tiles (M or N not a multiple of the tile); only
-// then is the per-sub-tile skipping compiled in.
+// then is the per-warp skipping compiled in.
 template <bool A_KCONTIG, bool B_KCONTIG, int SHAPE, bool EDGE, class Cfg>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                  GemmEpilogue ep, int M, int N, int K, int tiles_n, int heavy_tiles, int light_tiles,
-                 int splits, int kt_per_split, int *status) {
+                 int splits, int kt_per_split, int grouped_ab, int *status) {
   constexpr int BM = Cfg::BM, BN = Cfg::BN, MT = Cfg::MT, NT = Cfg::NT;
   constexpr int kStages = Cfg::STAGES, kStageBytes = Cfg::STAGE_BYTES, kTileBytes = Cfg::A_BYTES;
   extern __shared__ uint8_t smem_raw[];
@@ -292,13 +286,23 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
           tma_load_2d(a_dst, &mapA, k0, m0, bar);
         } else {
 #pragma unroll
-          for (int b = 0; b < BM / 16; b++) tma_load_2d(a_dst + b * 2048, &mapA, m0 + 16 * b, k0, bar);
+          if (grouped_ab & 1) {
+            tma_load_3d(a_dst, &mapA, 0, k0, m0 >> 4, bar);  // all 16-column groups in one copy
+          } else {
+            for (int b = 0; b < BM / 16; b++)
+              tma_load_2d(a_dst + b * 2048, &mapA, m0 + 16 * b, k0, bar);
+          }
         }
         if (B_KCONTIG) {
           tma_load_2d(b_dst, &mapB, k0, n0, bar);
         } else {
 #pragma unroll
-          for (int b = 0; b < BN / 16; b++) tma_load_2d(b_dst + b * 2048, &mapB, n0 + 16 * b, k0, bar);
+          if (grouped_ab & 2) {
+            tma_load_3d(b_dst, &mapB, 0, k0, n0 >> 4, bar);
+          } else {
+            for (int b = 0; b < BN / 16; b++)
+              tma_load_2d(b_dst + b * 2048, &mapB, n0 + 16 * b, k0, bar);
+          }
         }
       }
     }
@@ -319,27 +323,14 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
 #pragma unroll
         for (int r = 0; r < 4; r++) acc[i][j][r] = 0.0;
 
-    // Edge tiles: number of 16-row / 8-column sub-tiles of this warp that hold at
-    // least one in-range output.  Out-of-range sub-tiles are skipped entirely (no
-    // fragment loads, no MMAs), so a ragged edge — 784 rows, or the 10 logit columns
-    // — costs what it contains, not a full 128-wide tile.  Both counts are
-    // warp-uniform.
-    const int m_left = M - (m0 + wm), n_left = N - (n0 + wn);
-    const int mt_count = m_left <= 0 ? 0 : (m_left >= MT * 16 ? MT : (m_left + 15) >> 4);
-    const int nt_count = n_left <= 0 ? 0 : (n_left >= NT * 8 ? NT : (n_left + 7) >> 3);
-
-    // Interior tiles of a ragged problem run the same unguarded loop as a problem
-    // without edges; only the CTAs on the ragged border pay for the guards.
-    bool ok;
-    if (!EDGE || (mt_count == MT && nt_count == NT)) {
-      ok = consumer_loop<A_KCONTIG, B_KCONTIG, SHAPE, true, Cfg>(acc, smem, full_bar, empty_bar, nkt,
-                                                                  abort_flag, c0, g, wm, wn, lane,
-                                                                  MT, NT);
-    } else {
-      ok = consumer_loop<A_KCONTIG, B_KCONTIG, SHAPE, false, Cfg>(acc, smem, full_bar, empty_bar,
-                                                                   nkt, abort_flag, c0, g, wm, wn,
-                                                                   lane, mt_count, nt_count);
-    }
+    // Ragged border tiles: a warp whose whole sub-block lies outside the matrix
+    // does no arithmetic.  (Skipping at the granularity of single MMAs was
+    // measured to be slower than issuing them: the guards break up the
+    // instruction stream.)  Out-of-range rows and columns of a live warp read
+    // zeros from the TMA fill and are dropped in the epilogue.
+    const bool active = !EDGE || (M > m0 + wm && N > n0 + wn);
+    const bool ok = consumer_loop<A_KCONTIG, B_KCONTIG, SHAPE, Cfg>(
+        acc, smem, full_bar, empty_bar, nkt, abort_flag, c0, g, wm, wn, lane, active);
 
     if (ok) {
       // ---------------- epilogue ----------------
@@ -498,6 +489,7 @@ struct DmmaLaunch {
   CUtensorMap ma, mb;
   GemmEpilogue ep;
   int M, N, K, tiles_m, tiles_n, splits, kt_per_split;
+  int grouped_ab;  // bit 0 / bit 1: operand A / B uses the grouped 3-D tensor map
 };
 
 // A rectangle of tiles: rows [m0, m0 + rows), columns [n0, n0 + cols).
@@ -522,6 +514,7 @@ static int launch_dmma_kernel(const DmmaLaunch &L, const TileRegion &R) {
   dim3 grid((unsigned)(tiles * L.splits), 1, 1);
   kernel<<<grid, kGemmThreads, Cfg::SMEM_BYTES, c.stream>>>(L.ma, L.mb, L.ep, L.M, L.N, L.K, R.cols,
                                                              tiles - light, light, L.splits, L.kt_per_split,
+                                                             L.grouped_ab,
                                                              c.kernel_status);
   MG_LAUNCH_CHECK("dmma_gemm");
   return MG_OK;
@@ -585,13 +578,7 @@ struct GemmPlan {
 
 static GemmPlan choose_plan(int M, int N, int K, int sms, int shape) {
   const int KT = (K + BK - 1) / BK;
-  // Tiles that are at least half full decide how the waves fill up; the thin
-  // border tiles of a ragged problem are short and slot into the gaps.
-  auto tiles_of = [&](int bm, int bn) {
-    const int tm = (M % bm) * 2 >= bm ? (M + bm - 1) / bm : M / bm;
-    const int tn = (N % bn) * 2 >= bn ? (N + bn - 1) / bn : N / bn;
-    return (tm > 0 ? tm : 1) * (tn > 0 ? tn : 1);
-  };
+  auto tiles_of = [&](int bm, int bn) { return ((M + bm - 1) / bm) * ((N + bn - 1) / bn); };
   if (N <= SkinnyCfg::BN) {
     return {kTileSkinny, SkinnyCfg::BM, SkinnyCfg::BN,
             choose_splits(tiles_of(SkinnyCfg::BM, SkinnyCfg::BN), KT, sms)};
@@ -672,10 +659,27 @@ static int run_gemm(const GemmDesc &d) {
   const GemmPlan plan = choose_plan(M, N, K, c.sm_count, shape);
   const int bm = plan.bm, bn = plan.bn;
   DmmaLaunch L;
-  bool ok_a = d.a_kcontig ? make_tensor_map_f64(&L.ma, d.A, d.M, d.K, BK, bm)
-                          : make_tensor_map_f64(&L.ma, d.A, d.K, d.M, 16, BK);
-  bool ok_b = d.b_kcontig ? make_tensor_map_f64(&L.mb, d.B, d.N, d.K, BK, bn)
-                          : make_tensor_map_f64(&L.mb, d.B, d.K, d.N, 16, BK);
+  // Operands whose contiguous axis is m or n arrive as 16-column groups.  When the
+  // row length is a multiple of 16 one 3-D copy per stage brings all groups of the
+  // tile; otherwise each group is its own 2-D copy.
+  L.grouped_ab = 0;
+  bool ok_a, ok_b;
+  if (d.a_kcontig) {
+    ok_a = make_tensor_map_f64(&L.ma, d.A, d.M, d.K, BK, bm);
+  } else if (d.M % 16 == 0 && make_tensor_map_f64_grouped(&L.ma, d.A, d.K, d.M, BK, bm / 16)) {
+    ok_a = true;
+    L.grouped_ab |= 1;
+  } else {
+    ok_a = make_tensor_map_f64(&L.ma, d.A, d.K, d.M, 16, BK);
+  }
+  if (d.b_kcontig) {
+    ok_b = make_tensor_map_f64(&L.mb, d.B, d.N, d.K, BK, bn);
+  } else if (d.N % 16 == 0 && make_tensor_map_f64_grouped(&L.mb, d.B, d.K, d.N, BK, bn / 16)) {
+    ok_b = true;
+    L.grouped_ab |= 2;
+  } else {
+    ok_b = make_tensor_map_f64(&L.mb, d.B, d.K, d.N, 16, BK);
+  }
   if (!ok_a || !ok_b) return fail(MG_ERR_CUDA, "gemm: cuTensorMapEncodeTiled failed");
 
   const int tiles_m = (M + bm - 1) / bm, tiles_n = (N + bn - 1) / bn;

@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstdio>
+#include <cstdlib>
 
 namespace mg {
 
@@ -47,6 +49,28 @@ inline bool make_tensor_map_f64(CUtensorMap *map, const double *base, size_t row
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 2, const_cast<double *>(base), dims,
                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// The same matrix when cols is a multiple of 16, viewed as a 3-D tensor
+// (x = column within a 16-column group, y = row, z = column group) so that one
+// copy brings `box_groups` adjacent 16-column groups x `box_rows` rows: the
+// shared-memory image is `box_groups` consecutive [box_rows][16] swizzled
+// sub-tiles, identical to what box_groups separate 2-D copies produce.
+inline bool make_tensor_map_f64_grouped(CUtensorMap *map, const double *base, size_t rows,
+                                        size_t cols, unsigned box_rows, unsigned box_groups) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn || (cols % 16) != 0) return false;
+  cuuint64_t dims[3] = {16, (cuuint64_t)rows, (cuuint64_t)(cols / 16)};
+  cuuint64_t strides[2] = {(cuuint64_t)cols * sizeof(double), 16 * sizeof(double)};
+  cuuint32_t box[3] = {16, box_rows, box_groups};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 3, const_cast<double *>(base), dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS && getenv("MG_DEBUG"))
+    fprintf(stderr, "grouped tensor map rejected: CUresult %d (rows %zu cols %zu box %u x %u)\n",
+            (int)r, rows, cols, box_rows, box_groups);
   return r == CUDA_SUCCESS;
 }
 
@@ -119,6 +143,17 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, "
       "%4}], [%2];" ::"r"(smem_dst),
       "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+// 3-D form for the grouped view above: x is always 0, y the first row, z the
+// first 16-column group.
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap *map, int x, int y,
+                                            int z, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, "
+      "%4, %5}], [%2];" ::"r"(smem_dst),
+      "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
 
