@@ -266,8 +266,11 @@ def run_product(args):
     # ---- roofline of the dominant kernel, timed alone (rank 0) ----
     roofline = None
     cpu_baseline = None
+    sweeps = None
     if rank == 0:
         roofline = gemm_roofline(abi, K, rows)
+        if world == 1 and not args.no_sweeps:
+            sweeps = metric_sweeps(abi, K)
         if world == 1 and not args.no_cpu_baseline:
             cpu_baseline = reference_sample(budget_s=20.0)
 
@@ -297,6 +300,7 @@ def run_product(args):
         "gpu_launches": int(launches),
         "roofline": roofline,
         "cpu_baseline": cpu_baseline,
+        "sweeps": sweeps,
     }
     print(json.dumps(out), flush=True)
 
@@ -335,6 +339,56 @@ def gemm_roofline(abi, K, rows):
             "peak_nominal": NOMINAL_FP64_TFLOPS, "frac_of_nominal": achieved / NOMINAL_FP64_TFLOPS,
             "ms_per_launch": ms, "flop_per_launch": 2.0 * M * N * Kd, "dmma_probe_tflops": probe,
             "traffic": None}
+
+
+def metric_sweeps(abi, K):
+    """The other two parts of the BASELINE metric, measured on one GPU with events:
+    DGEMM TFLOP/s (forward C = A.B; BASELINE config 3 shapes) and elementwise /
+    reduction GB/s (BASELINE config 2 ops at 2^24 and 2^28 elements, algorithmic
+    bytes per element: binary forward 24, unary forward 16, sums 8).  Arrays are
+    far larger than L2 at both sizes."""
+    rng = np.random.default_rng(11)
+    seed = abi.array(rng.standard_normal(1 << 22))
+
+    def filled(n):
+        buf = abi.empty(n)
+        for off in range(0, n, 1 << 22):
+            abi.mg_copy(buf.offset(off), seed.ptr, min(1 << 22, n - off))
+        return buf
+
+    def timed(fn, reps):
+        for _ in range(2):
+            fn()
+        return abi.timed_ms(fn, reps) / reps
+
+    out = {"dgemm_tflops": {}, "elementwise_gbs": {}}
+    for tag, (m, n, k), reps in (("1024^3", (1024, 1024, 1024), 20), ("4096^3", (4096, 4096, 4096), 3),
+                                 ("8192^3", (8192, 8192, 8192), 2),
+                                 ("65536x784.784x1024", (65536, 1024, 784), 3)):
+        a, b, c = filled(m * k), filled(k * n), abi.empty(m * n)
+        ms = timed(lambda: abi.mg_gemm_nn(a.ptr, b.ptr, c.ptr, m, n, k, 0, K.EPI_NONE, None), reps)
+        out["dgemm_tflops"][tag] = round(2.0 * m * n * k / ms / 1e9, 2)
+        del a, b, c
+    for log2n in (24, 28):
+        n = 1 << log2n
+        a, b, g, o = filled(n), filled(n), filled(n), abi.empty(n)
+        side = 1 << (log2n // 2)
+        ops = (("add", lambda: abi.mg_binary_fwd(K.ADD, a.ptr, b.ptr, o.ptr, n), 24),
+               ("mul", lambda: abi.mg_binary_fwd(K.MUL, a.ptr, b.ptr, o.ptr, n), 24),
+               ("sub", lambda: abi.mg_binary_fwd(K.SUB, a.ptr, b.ptr, o.ptr, n), 24),
+               ("relu", lambda: abi.mg_unary_fwd(K.RELU, a.ptr, 0.0, o.ptr, n), 16),
+               ("tanh", lambda: abi.mg_unary_fwd(K.TANH, a.ptr, 0.0, o.ptr, n), 16),
+               ("exp", lambda: abi.mg_unary_fwd(K.EXP, a.ptr, 0.0, o.ptr, n), 16),
+               ("add_row", lambda: abi.mg_add_row_fwd(a.ptr, b.ptr, o.ptr, side, side), 16),
+               ("sum", lambda: abi.mg_sum_all_fwd(a.ptr, o.ptr, n), 8),
+               ("sum_lastaxis", lambda: abi.mg_sum_lastaxis_fwd(a.ptr, o.ptr, side, side), 8),
+               ("mul_bwd_one_side", lambda: abi.mg_binary_bwd(K.MUL, a.ptr, b.ptr, g.ptr, o.ptr, None,
+                                                               n, 0), 40))
+        for name, fn, bytes_per in ops:
+            ms = timed(fn, 5)
+            out["elementwise_gbs"][f"{name}@2^{log2n}"] = round(bytes_per * n / ms / 1e6, 1)
+        del a, b, g, o
+    return out
 
 
 # --------------------------------------------------------------------------- reference arm
@@ -407,6 +461,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch (default: config 4)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sweeps", action="store_true",
+                    help="skip the DGEMM / elementwise sweeps that fill the `sweeps` key")
     ap.add_argument("--sync-each-step", action="store_true",
                     help="diagnostic: host waits for the device after every step")
     ap.add_argument("--value-only", action="store_true",

@@ -332,11 +332,44 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     const bool ok = consumer_loop<A_KCONTIG, B_KCONTIG, SHAPE, Cfg>(
         acc, smem, full_bar, empty_bar, nkt, abort_flag, c0, g, wm, wn, lane, active);
 
-    if (ok) {
+    if (ok && active) {
       // ---------------- epilogue ----------------
+      // Per 16-row sub-tile: first every global load the epilogue needs (ReLU mask
+      // source, old values for accumulation) is issued, then the arithmetic, then
+      // the stores.  Interleaving load/store pairs would serialise them (a store
+      // may alias the next load as far as the compiler can tell) and turn the
+      // epilogue into a chain of exposed memory latencies.
       double *dst = ep.partial ? ep.partial + (size_t)split * (size_t)M * (size_t)N : ep.D;
+      const bool direct = (ep.partial == nullptr);
+      const bool use_mask = direct && ep.mode == MG_EPI_RELU_MASK;
+      const bool use_bias = direct && (ep.mode == MG_EPI_BIAS || ep.mode == MG_EPI_BIAS_RELU);
+      const bool use_old = direct && ep.accumulate;
+      double2 bias[NT];
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++) {
+        const int col = n0 + wn + nt * 8 + 2 * t;
+        bias[nt] = make_double2(0.0, 0.0);
+        if (use_bias && col < N) bias[nt] = make_double2(__ldg(ep.aux + col), __ldg(ep.aux + col + 1));
+      }
 #pragma unroll
       for (int mt = 0; mt < MT; mt++) {
+        double2 mask[2][NT], old[2][NT];
+        if (use_mask || use_old) {
+#pragma unroll
+          for (int h = 0; h < 2; h++) {
+            const int row = m0 + wm + mt * 16 + g + 8 * h;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+              const int col = n0 + wn + nt * 8 + 2 * t;
+              const bool in = row < M && col < N;
+              const size_t at = (size_t)row * (size_t)N + (size_t)col;
+              mask[h][nt] = (use_mask && in) ? __ldcs(reinterpret_cast<const double2 *>(ep.aux + at))
+                                             : make_double2(0.0, 0.0);
+              old[h][nt] = (use_old && in) ? __ldcs(reinterpret_cast<const double2 *>(ep.D + at))
+                                           : make_double2(0.0, 0.0);
+            }
+          }
+        }
 #pragma unroll
         for (int h = 0; h < 2; h++) {
           const int row = m0 + wm + mt * 16 + g + 8 * h;
@@ -347,7 +380,22 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
             if (col >= N) continue;
             const size_t at = (size_t)row * (size_t)N + (size_t)col;
             double2 v = make_double2(acc[mt][nt][2 * h], acc[mt][nt][2 * h + 1]);
-            if (!ep.partial) v = apply_epilogue(v, ep, at, col);
+            if (use_bias) {
+              v.x += bias[nt].x;
+              v.y += bias[nt].y;
+              if (ep.mode == MG_EPI_BIAS_RELU) {
+                v.x = v.x > 0 ? v.x : 0.0;
+                v.y = v.y > 0 ? v.y : 0.0;
+              }
+            }
+            if (use_mask) {
+              v.x = v.x * (mask[h][nt].x > 0 ? 1.0 : 0.0);
+              v.y = v.y * (mask[h][nt].y > 0 ? 1.0 : 0.0);
+            }
+            if (use_old) {
+              v.x = old[h][nt].x + v.x;
+              v.y = old[h][nt].y + v.y;
+            }
             *reinterpret_cast<double2 *>(dst + at) = v;
           }
         }

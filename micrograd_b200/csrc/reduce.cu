@@ -190,13 +190,17 @@ colsum_partial_kernel(const double *__restrict__ g, double *__restrict__ gx, boo
   }
 }
 
+// One warp per column: lane l folds partials l, l+32, ... in index order, then a
+// butterfly over the lanes — a fixed order, so the result is reproducible.
 __global__ void colsum_finish_kernel(const double *__restrict__ partials, size_t S, size_t N,
                                      double *__restrict__ out, bool accumulate) {
-  const size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane_id = threadIdx.x & 31;
+  const size_t j = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (j >= N) return;
-  double t = accumulate ? out[j] : 0.0;
-  for (size_t s = 0; s < S; s++) t += partials[s * N + j];
-  out[j] = t;
+  double t = 0.0;
+  for (size_t s = lane_id; s < S; s += 32) t += partials[s * N + j];
+  t = warp_sum(t);
+  if (lane_id == 0) out[j] = accumulate ? out[j] + t : t;
 }
 
 // ---------------------------------------------------------------------------
@@ -381,7 +385,7 @@ int mg_add_row_bwd(const double *g, double *gx, double *grow, size_t M, size_t N
       colsum_partial_kernel<1, 8><<<grid, 256, 0, c.stream>>>(g, gx, gx_acc, c.colsum_scratch, M, N, rows_per_chunk);
   }
   MG_LAUNCH_CHECK("colsum_partial");
-  colsum_finish_kernel<<<(unsigned)((N + 255) / 256), 256, 0, c.stream>>>(
+  colsum_finish_kernel<<<(unsigned)((N * 32 + 255) / 256), 256, 0, c.stream>>>(
       c.colsum_scratch, S, N, grow, !(flags & MG_ACC_STORE_B));
   MG_LAUNCH_CHECK("colsum_finish");
   return MG_OK;
@@ -521,7 +525,7 @@ extern "C" int mg_colsum_noalloc(const double *g, double *out_row, size_t M, siz
       colsum_partial_kernel<1, 8><<<grid, 256, 0, c.stream>>>(g, nullptr, false, scratch, M, N, rows_per_chunk);
   }
   MG_LAUNCH_CHECK("colsum_partial (static scratch)");
-  colsum_finish_kernel<<<(unsigned)((N + 255) / 256), 256, 0, c.stream>>>(scratch, S, N, out_row,
+  colsum_finish_kernel<<<(unsigned)((N * 32 + 255) / 256), 256, 0, c.stream>>>(scratch, S, N, out_row,
                                                                           accumulate != 0);
   MG_LAUNCH_CHECK("colsum_finish (static scratch)");
   return MG_OK;
