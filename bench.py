@@ -74,6 +74,8 @@ class ClockSampler:
         self.index, self.rows, self.proc, self.thread = index, [], None, None
 
     def start(self):
+        if os.environ.get("MG_BENCH_NO_SAMPLER"):
+            return
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",

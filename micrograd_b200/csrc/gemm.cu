@@ -59,6 +59,11 @@ using SkinnyCfg = TileCfg<1, 1, 4, 8>;
 // 128 x 64, eight 24 KB stages: used when 128 x 128 tiles would leave the last
 // wave of CTAs mostly empty (e.g. 512 tiles on 148 SMs).
 using HalfCfg = TileCfg<2, 2, 4, 8>;
+// 112 x 128, six 30 KB stages: eight warps side by side, each 112 rows x 16
+// columns.  For outputs whose row count is a multiple of 112 but not of 128
+// (784 = 7 x 112, the MNIST-sized input layer's weight gradient), where 128-row
+// tiles would spend an eighth of the machine on padding.
+using Rows112Cfg = TileCfg<8, 7, 2, 6>;
 
 struct GemmEpilogue {
   double *D;            // output [M][N]
@@ -194,11 +199,13 @@ __device__ __forceinline__ void compute_stage(double (&acc)[MT][NT][4], const ui
 template <bool A_KCONTIG, bool B_KCONTIG, int SHAPE, class Cfg>
 __device__ __forceinline__ bool consumer_loop(double (&acc)[Cfg::MT][Cfg::NT][4], const uint8_t *smem,
                                               uint64_t *full_bar, uint64_t *empty_bar, int nkt,
-                                              volatile int *abort_flag, int c0, int g, int wm, int wn,
-                                              int lane, bool active) {
-  for (int it = 0; it < nkt; ++it) {
-    const int s = it % Cfg::STAGES;
-    if (!mbar_wait_bounded(smem_u32(full_bar + s), (it / Cfg::STAGES) & 1, abort_flag)) return false;
+                                              unsigned &ring, volatile int *abort_flag, int c0, int g,
+                                              int wm, int wn, int lane, bool active) {
+  // `ring` counts stages consumed by this CTA since it started; it runs on across
+  // the tiles a persistent CTA processes, so stage index and barrier phase follow.
+  for (int it = 0; it < nkt; ++it, ++ring) {
+    const unsigned s = ring % Cfg::STAGES;
+    if (!mbar_wait_bounded(smem_u32(full_bar + s), (ring / Cfg::STAGES) & 1, abort_flag)) return false;
     const uint8_t *As = smem + s * Cfg::STAGE_BYTES;
     const uint8_t *Bs = As + Cfg::A_BYTES;
     if (active)
@@ -212,11 +219,52 @@ __device__ __forceinline__ bool consumer_loop(double (&acc)[Cfg::MT][Cfg::NT][4]
 // SHAPE: 0 m8n8k4, 1 m16n8k4, 2 m16n8k8, 3 m16n8k16.
 // EDGE: the problem has ragged tiles (M or N not a multiple of the tile); only
 // then is the per-warp skipping compiled in.
-template <bool A_KCONTIG, bool B_KCONTIG, int SHAPE, bool EDGE, class Cfg>
+// One unit of work of a launch: an output tile and a range of k-tiles.
+struct WorkItem {
+  int m0, n0, kt_begin, nkt, split;
+};
+
+// Work order.  Tiles are numbered row-major; the first `heavy_tiles` of them are
+// (at least half) full, the remaining `light_tiles` are the thin bottom border of
+// a ragged problem.  Items are issued split by split over the heavy tiles (CTAs
+// working at the same time then share one k-range of both operands in L2), and
+// all light tiles come last, so that short items fill the tail instead of
+// pushing full ones into an extra round.
+template <class Cfg>
+__device__ __forceinline__ WorkItem decode_work(int id, int tiles_n, int heavy_tiles, int light_tiles,
+                                                int splits, int kt_per_split, int KT) {
+  int tile, split;
+  const int heavy_items = heavy_tiles * splits;
+  if (id < heavy_items) {
+    split = id / heavy_tiles;
+    tile = id - split * heavy_tiles;
+  } else {
+    const int j = id - heavy_items;
+    split = j / light_tiles;
+    tile = heavy_tiles + (j - split * light_tiles);
+  }
+  const int tile_m = tile / tiles_n, tile_n = tile - tile_m * tiles_n;
+  WorkItem w;
+  w.m0 = tile_m * Cfg::BM;
+  w.n0 = tile_n * Cfg::BN;
+  w.split = split;
+  w.kt_begin = split * kt_per_split;
+  w.nkt = min(KT, w.kt_begin + kt_per_split) - w.kt_begin;
+  return w;
+}
+
+// PERSISTENT: the grid has at most one CTA per SM and CTA b processes work items
+// b, b + gridDim.x, ...; the producer runs ahead into the next item while the
+// consumers are still in the epilogue of the current one, so the pipeline fill
+// of an item is hidden behind the previous item's stores.  Used for short items
+// (skinny or shallow problems).  Otherwise every CTA processes exactly one item
+// and the hardware scheduler balances the load; the loop below then compiles to
+// straight-line code, which keeps the consumer's register budget free of spills.
+template <bool A_KCONTIG, bool B_KCONTIG, int SHAPE, bool EDGE, class Cfg, bool PERSISTENT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                  GemmEpilogue ep, int M, int N, int K, int tiles_n, int heavy_tiles, int light_tiles,
-                 int splits, int kt_per_split, int grouped_ab, int *status) {
+                 int splits, int kt_per_split, int grouped_ab, int total_items, int *status) {
   constexpr int BM = Cfg::BM, BN = Cfg::BN, MT = Cfg::MT, NT = Cfg::NT;
   constexpr int kStages = Cfg::STAGES, kStageBytes = Cfg::STAGE_BYTES, kTileBytes = Cfg::A_BYTES;
   extern __shared__ uint8_t smem_raw[];
@@ -229,31 +277,7 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
   uint64_t *empty_bar = full_bar + kStages;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // Work order.  Tiles are numbered row-major; the first `heavy_tiles` of them are
-  // (at least half) full, the remaining `light_tiles` are the thin bottom border
-  // of a ragged problem.  CTAs are issued split by split over the heavy tiles
-  // (CTAs of one wave then share the same k-range of both operands in L2), and
-  // all light tiles come last, so that short CTAs fill the tail of the last
-  // wave instead of pushing full ones into an extra wave.
-  int tile, split;
-  {
-    const int id = blockIdx.x;
-    const int heavy_ctas = heavy_tiles * splits;
-    if (id < heavy_ctas) {
-      split = id / heavy_tiles;
-      tile = id - split * heavy_tiles;
-    } else {
-      const int j = id - heavy_ctas;
-      split = j / light_tiles;
-      tile = heavy_tiles + (j - split * light_tiles);
-    }
-  }
-  const int tile_m = tile / tiles_n, tile_n = tile - tile_m * tiles_n;
-  const int m0 = tile_m * BM, n0 = tile_n * BN;
   const int KT = (K + BK - 1) / BK;
-  const int kt_begin = split * kt_per_split;
-  const int kt_end = min(KT, kt_begin + kt_per_split);
-  const int nkt = kt_end - kt_begin;
 
   if (threadIdx.x == 0) {
     abort_flag_s = 0;
@@ -271,40 +295,45 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     if (warp == kConsumerWarps && lane == 0) {
       prefetch_tensormap(&mapA);
       prefetch_tensormap(&mapB);
-      for (int it = 0; it < nkt; ++it) {
-        const int s = it % kStages;
-        if (it >= kStages) {
-          if (!mbar_wait_bounded(smem_u32(empty_bar + s), ((it / kStages) - 1) & 1, abort_flag))
-            break;
-        }
-        const uint32_t bar = smem_u32(full_bar + s);
-        mbar_arrive_expect_tx(bar, kStageBytes);
-        const int k0 = (kt_begin + it) * BK;
-        const uint32_t a_dst = smem_u32(smem + s * kStageBytes);
-        const uint32_t b_dst = a_dst + kTileBytes;
-        if (A_KCONTIG) {
-          tma_load_2d(a_dst, &mapA, k0, m0, bar);
-        } else {
-#pragma unroll
-          if (grouped_ab & 1) {
-            tma_load_3d(a_dst, &mapA, 0, k0, m0 >> 4, bar);  // all 16-column groups in one copy
+      unsigned ring = 0;  // stages issued by this CTA so far
+      bool alive = true;
+      int id = blockIdx.x;
+      do {
+        const WorkItem w =
+            decode_work<Cfg>(id, tiles_n, heavy_tiles, light_tiles, splits, kt_per_split, KT);
+        for (int it = 0; it < w.nkt; ++it, ++ring) {
+          const unsigned s = ring % kStages;
+          if (ring >= (unsigned)kStages) {
+            if (!mbar_wait_bounded(smem_u32(empty_bar + s), ((ring / kStages) - 1) & 1, abort_flag)) {
+              alive = false;
+              break;
+            }
+          }
+          const uint32_t bar = smem_u32(full_bar + s);
+          mbar_arrive_expect_tx(bar, kStageBytes);
+          const int k0 = (w.kt_begin + it) * BK;
+          const uint32_t a_dst = smem_u32(smem + s * kStageBytes);
+          const uint32_t b_dst = a_dst + kTileBytes;
+          if (A_KCONTIG) {
+            tma_load_2d(a_dst, &mapA, k0, w.m0, bar);
+          } else if (grouped_ab & 1) {
+            tma_load_3d(a_dst, &mapA, 0, k0, w.m0 >> 4, bar);  // all 16-column groups in one copy
           } else {
             for (int b = 0; b < BM / 16; b++)
-              tma_load_2d(a_dst + b * 2048, &mapA, m0 + 16 * b, k0, bar);
+              tma_load_2d(a_dst + b * 2048, &mapA, w.m0 + 16 * b, k0, bar);
           }
-        }
-        if (B_KCONTIG) {
-          tma_load_2d(b_dst, &mapB, k0, n0, bar);
-        } else {
-#pragma unroll
-          if (grouped_ab & 2) {
-            tma_load_3d(b_dst, &mapB, 0, k0, n0 >> 4, bar);
+          if (B_KCONTIG) {
+            tma_load_2d(b_dst, &mapB, k0, w.n0, bar);
+          } else if (grouped_ab & 2) {
+            tma_load_3d(b_dst, &mapB, 0, k0, w.n0 >> 4, bar);
           } else {
             for (int b = 0; b < BN / 16; b++)
-              tma_load_2d(b_dst + b * 2048, &mapB, n0 + 16 * b, k0, bar);
+              tma_load_2d(b_dst + b * 2048, &mapB, w.n0 + 16 * b, k0, bar);
           }
         }
-      }
+        if (!PERSISTENT) break;
+        id += gridDim.x;
+      } while (alive && id < total_items);
     }
   } else {
     // ---------------- consumer warp groups ----------------
@@ -314,25 +343,33 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     // 16-byte chunk owned by this thread in the first half-slab; the second
     // half-slab uses chunk ^ 1.
     const int c0 = (t << 1) | (__popc(t) & 1);
+    unsigned ring = 0;  // stages consumed by this CTA so far
 
-    double acc[MT][NT][4];
-#pragma unroll
-    for (int i = 0; i < MT; i++)
-#pragma unroll
-      for (int j = 0; j < NT; j++)
-#pragma unroll
-        for (int r = 0; r < 4; r++) acc[i][j][r] = 0.0;
+    int id = blockIdx.x;
+    do {
+      const WorkItem w =
+          decode_work<Cfg>(id, tiles_n, heavy_tiles, light_tiles, splits, kt_per_split, KT);
+      const int m0 = w.m0, n0 = w.n0, split = w.split;
 
-    // Ragged border tiles: a warp whose whole sub-block lies outside the matrix
-    // does no arithmetic.  (Skipping at the granularity of single MMAs was
-    // measured to be slower than issuing them: the guards break up the
-    // instruction stream.)  Out-of-range rows and columns of a live warp read
-    // zeros from the TMA fill and are dropped in the epilogue.
-    const bool active = !EDGE || (M > m0 + wm && N > n0 + wn);
-    const bool ok = consumer_loop<A_KCONTIG, B_KCONTIG, SHAPE, Cfg>(
-        acc, smem, full_bar, empty_bar, nkt, abort_flag, c0, g, wm, wn, lane, active);
+      double acc[MT][NT][4];
+#pragma unroll
+      for (int i = 0; i < MT; i++)
+#pragma unroll
+        for (int j = 0; j < NT; j++)
+#pragma unroll
+          for (int r = 0; r < 4; r++) acc[i][j][r] = 0.0;
 
-    if (ok && active) {
+      // Ragged border tiles: a warp whose whole sub-block lies outside the matrix
+      // does no arithmetic.  (Skipping at the granularity of single MMAs was
+      // measured to be slower than issuing them: the guards break up the
+      // instruction stream.)  Out-of-range rows and columns of a live warp read
+      // zeros from the TMA fill and are dropped in the epilogue.
+      const bool active = !EDGE || (M > m0 + wm && N > n0 + wn);
+      const bool ok = consumer_loop<A_KCONTIG, B_KCONTIG, SHAPE, Cfg>(
+          acc, smem, full_bar, empty_bar, w.nkt, ring, abort_flag, c0, g, wm, wn, lane, active);
+      if (!ok) break;
+      if (active) {
+
       // ---------------- epilogue ----------------
       // Per 16-row sub-tile: first every global load the epilogue needs (ReLU mask
       // source, old values for accumulation) is issued, then the arithmetic, then
@@ -400,7 +437,10 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
           }
         }
       }
-    }
+      }  // active
+      if (!PERSISTENT) break;
+      id += gridDim.x;
+    } while (id < total_items);
   }
 
   // A bounded wait gave up somewhere in this CTA: raise the fault word, give the
@@ -545,11 +585,10 @@ struct TileRegion {
   int m0, n0, rows, cols;
 };
 
-template <bool AK, bool BK_, int SHAPE, bool EDGE, class Cfg>
-static int launch_dmma_kernel(const DmmaLaunch &L, const TileRegion &R) {
-  if (R.rows <= 0 || R.cols <= 0) return MG_OK;
+template <bool AK, bool BK_, int SHAPE, bool EDGE, class Cfg, bool PERSISTENT>
+static int launch_dmma_variant(const DmmaLaunch &L, const TileRegion &R) {
   static bool configured = false;
-  auto kernel = dmma_gemm_kernel<AK, BK_, SHAPE, EDGE, Cfg>;
+  auto kernel = dmma_gemm_kernel<AK, BK_, SHAPE, EDGE, Cfg, PERSISTENT>;
   if (!configured) {
     MG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      Cfg::SMEM_BYTES));
@@ -559,13 +598,33 @@ static int launch_dmma_kernel(const DmmaLaunch &L, const TileRegion &R) {
   const int tiles = R.rows * R.cols;
   // bottom row of tiles less than half full -> its tiles are "light"
   const int light = ((L.M % Cfg::BM) != 0 && (L.M % Cfg::BM) * 2 < Cfg::BM && R.rows > 1) ? R.cols : 0;
-  dim3 grid((unsigned)(tiles * L.splits), 1, 1);
+  const int items = tiles * L.splits;
+  // Long items (many k-tiles) are left to the hardware scheduler, one item per
+  // CTA: it balances them dynamically.  Short items (skinny or shallow problems)
+  // run as a persistent grid, where the cross-item prefetch hides the pipeline
+  // fill that would otherwise dominate them.
+  dim3 grid((unsigned)((PERSISTENT && items > c.sm_count) ? c.sm_count : items), 1, 1);
   kernel<<<grid, kGemmThreads, Cfg::SMEM_BYTES, c.stream>>>(L.ma, L.mb, L.ep, L.M, L.N, L.K, R.cols,
-                                                             tiles - light, light, L.splits, L.kt_per_split,
-                                                             L.grouped_ab,
+                                                             tiles - light, light, L.splits,
+                                                             L.kt_per_split, L.grouped_ab, items,
                                                              c.kernel_status);
   MG_LAUNCH_CHECK("dmma_gemm");
   return MG_OK;
+}
+
+template <bool AK, bool BK_, int SHAPE, bool EDGE, class Cfg>
+static int launch_dmma_kernel(const DmmaLaunch &L, const TileRegion &R) {
+  if (R.rows <= 0 || R.cols <= 0) return MG_OK;
+  static const int persist_mode = [] {
+    const char *v = std::getenv("MG_GEMM_PERSIST");  // diagnostic: 0 never, 1 always
+    return v && *v ? std::atoi(v) : -1;
+  }();
+  bool persistent = (L.kt_per_split < 32 || Cfg::BN <= 32) &&
+                    R.rows * R.cols * L.splits > ctx().sm_count;
+  if (persist_mode == 0) persistent = false;
+  if (persist_mode == 1) persistent = true;
+  if (persistent) return launch_dmma_variant<AK, BK_, SHAPE, EDGE, Cfg, true>(L, R);
+  return launch_dmma_variant<AK, BK_, SHAPE, EDGE, Cfg, false>(L, R);
 }
 
 // One launch over all tiles; problems with a ragged border use the instantiation
@@ -578,7 +637,7 @@ static int launch_regions(const DmmaLaunch &L) {
   return launch_dmma_kernel<AK, BK_, SHAPE, false, Cfg>(L, all);
 }
 
-enum TileChoice { kTileMain = 0, kTileSkinny = 1, kTileHalf = 2 };
+enum TileChoice { kTileMain = 0, kTileSkinny = 1, kTileHalf = 2, kTileRows112 = 3 };
 
 template <bool AK, bool BK_>
 static int launch_layout(int shape, int tile, const DmmaLaunch &L) {
@@ -586,6 +645,7 @@ static int launch_layout(int shape, int tile, const DmmaLaunch &L) {
   if (tile == kTileSkinny)
     return launch_dmma_kernel<AK, BK_, 2, true, SkinnyCfg>(L, TileRegion{0, 0, L.tiles_m, L.tiles_n});
   if (tile == kTileHalf) return launch_regions<AK, BK_, 2, HalfCfg>(L);
+  if (tile == kTileRows112) return launch_regions<AK, BK_, 2, Rows112Cfg>(L);
   switch (shape) {
     case 0: return launch_regions<AK, BK_, 0, MainCfg>(L);
     case 1: return launch_regions<AK, BK_, 1, MainCfg>(L);
@@ -650,7 +710,14 @@ static GemmPlan choose_plan(int M, int N, int K, int sms, int shape) {
     if (p.splits > 1) c *= 1.0 + 22.8 * (p.splits + 1) / (double)K;
     return c;
   };
-  return cost(half_plan, 1.04) < cost(main_plan, 1.0) ? half_plan : main_plan;
+  GemmPlan best = cost(half_plan, 1.04) < cost(main_plan, 1.0) ? half_plan : main_plan;
+  double best_cost = best.tile == kTileHalf ? cost(half_plan, 1.04) : cost(main_plan, 1.0);
+  if (M % MainCfg::BM != 0 && M % Rows112Cfg::BM == 0) {
+    GemmPlan p112{kTileRows112, Rows112Cfg::BM, Rows112Cfg::BN,
+                  choose_splits(tiles_of(Rows112Cfg::BM, Rows112Cfg::BN), KT, sms)};
+    if (cost(p112, 1.02) < best_cost) best = p112;
+  }
+  return best;
 }
 
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }

@@ -20,7 +20,7 @@ TOL = 1e-10
 # (M, K, N): tiny, odd (fallback kernel), tile-exact, ragged edges, skinny, deep
 SHAPES = [(1, 1, 1), (2, 2, 2), (5, 7, 4), (33, 17, 9), (32, 48, 16), (64, 64, 64), (128, 128, 128),
           (256, 256, 256), (200, 136, 72), (130, 18, 258), (1024, 256, 10), (512, 10, 512),
-          (300, 784, 128), (96, 1040, 192)]
+          (300, 784, 128), (96, 1040, 192), (784, 40, 256), (112, 16, 48), (1568, 64, 1024)]
 PATHS = [1, 2]  # 1: plain tiled kernel, 2: tensor-core kernel whenever operands allow
 
 
