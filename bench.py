@@ -64,18 +64,37 @@ def make_batch(rows, seed):
 
 # --------------------------------------------------------------------------- clocks
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while a region runs."""
+    """Samples SM clock, power and throttle reasons while a region runs.
+
+    Uses NVML in-process (a light query every 100 ms from a thread); falls back to
+    an `nvidia-smi -lms` child process when the NVML binding is unavailable.
+    MG_BENCH_SAMPLER=smi|nvml|none overrides the choice."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index):
         self.index, self.rows, self.proc, self.thread = index, [], None, None
+        self.mode = os.environ.get("MG_BENCH_SAMPLER", "nvml")
+        self._stop = threading.Event()
 
     def start(self):
-        if os.environ.get("MG_BENCH_NO_SAMPLER"):
+        if self.mode == "none":
             return
+        if self.mode == "nvml":
+            try:
+                import pynvml
+                pynvml.nvmlInit()
+                self._nvml = pynvml
+                self._handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+                self._max = float(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+                self.thread = threading.Thread(target=self._poll_nvml, daemon=True)
+                self.thread.start()
+                return
+            except Exception:
+                self.mode = "smi"
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
@@ -87,29 +106,51 @@ class ClockSampler:
         self.thread = threading.Thread(target=self._pump, daemon=True)
         self.thread.start()
 
+    def _poll_nvml(self):
+        nv = self._nvml
+        bits = {"hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+                "sw_power_cap": 0x4}
+        while not self._stop.is_set():
+            try:
+                sm = float(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM))
+                pw = nv.nvmlDeviceGetPowerUsage(self._handle) / 1000.0
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._handle)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle)
+                flags = ["Active" if mask & bits[n] else "Not Active" for n in self.NAMES]
+                self.rows.append([str(sm), str(self._max), str(pw)] + flags)
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
     def _pump(self):
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def stop(self):
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        if self.mode == "none" or (self.proc is None and self.thread is None):
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["sampler unavailable"]}
         time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm = [float(r[0]) for r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) >= 7 and r[1].replace(".", "").isdigit()]
-        pw = [float(r[2]) for r in self.rows if len(r) >= 7 and r[2].replace(".", "").isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names)
+        self._stop.set()
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        elif self.thread:
+            self.thread.join(timeout=2)
+        ok = lambda v: v.replace(".", "").isdigit()
+        sm = [float(r[0]) for r in self.rows if len(r) >= 7 and ok(r[0])]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 7 and ok(r[1])]
+        pw = [float(r[2]) for r in self.rows if len(r) >= 7 and ok(r[2])]
+        reasons = [n for i, n in enumerate(self.NAMES)
                    if any(len(r) >= 7 and r[3 + i].lower().startswith("active") for r in self.rows)]
         return {"sm_mhz": float(np.median(sm)) if sm else None,
                 "sm_max_mhz": max(mx) if mx else None,
                 "power_w_max": max(pw) if pw else None,
-                "samples": len(sm), "reasons": reasons}
+                "samples": len(sm), "sampler": self.mode, "reasons": reasons}
 
 
 # --------------------------------------------------------------------------- product arm
