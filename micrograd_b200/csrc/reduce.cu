@@ -154,20 +154,49 @@ colsum_partial_kernel(const double *__restrict__ g, double *__restrict__ gx, boo
 #pragma unroll
   for (int l = 0; l < VEC; l++) acc[l] = 0.0;
   if (cv < ncol) {
-    for (size_t r = r0 + ty; r < r1; r += TY) {
-      const size_t at = r * ncol + cv;
-      if (VEC == 2) {
-        double2 v = __ldcs(reinterpret_cast<const double2 *>(g) + at);
+    if (VEC == 2) {
+      // Four rows per trip, all loads issued before the first store, so a thread
+      // keeps 4-8 independent 16-byte requests in flight.
+      const double2 *gv = reinterpret_cast<const double2 *>(g);
+      double2 *xv = reinterpret_cast<double2 *>(gx);
+      size_t r = r0 + ty;
+      for (; r + 3 * TY < r1; r += 4 * TY) {
+        double2 v[4], o[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) v[u] = __ldcs(gv + (r + u * TY) * ncol + cv);
+        if (gx && gx_accumulate) {
+#pragma unroll
+          for (int u = 0; u < 4; u++) o[u] = __ldcs(xv + (r + u * TY) * ncol + cv);
+        } else {
+#pragma unroll
+          for (int u = 0; u < 4; u++) o[u] = make_double2(0.0, 0.0);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          acc[0] += v[u].x;
+          acc[VEC - 1] += v[u].y;
+          if (gx) {
+            o[u].x += v[u].x;
+            o[u].y += v[u].y;
+            __stcs(xv + (r + u * TY) * ncol + cv, o[u]);
+          }
+        }
+      }
+      for (; r < r1; r += TY) {
+        const size_t at = r * ncol + cv;
+        double2 v = __ldcs(gv + at);
         acc[0] += v.x;
         acc[VEC - 1] += v.y;
         if (gx) {
-          double2 *p = reinterpret_cast<double2 *>(gx) + at;
-          double2 o = gx_accumulate ? __ldcs(p) : make_double2(0.0, 0.0);
+          double2 o = gx_accumulate ? __ldcs(xv + at) : make_double2(0.0, 0.0);
           o.x += v.x;
           o.y += v.y;
-          __stcs(p, o);
+          __stcs(xv + at, o);
         }
-      } else {
+      }
+    } else {
+      for (size_t r = r0 + ty; r < r1; r += TY) {
+        const size_t at = r * ncol + cv;
         double v = __ldcs(g + at);
         acc[0] += v;
         if (gx) {
