@@ -1,11 +1,12 @@
 // Elementwise forward/backward kernels, row-broadcast add, SGD update, fill.
 //
 // All of these are HBM-bound streaming kernels: one generic grid-stride "map"
-// kernel moves 16-byte vectors (two doubles) with four independent vectors in
-// flight per thread, and a small functor supplies the arithmetic.  The grid is
-// a whole number of waves (SM count x resident CTAs), each thread striding
-// through the array so that consecutive threads touch consecutive 16-byte
-// words.
+// kernel moves 32-byte vectors (four doubles, the 256-bit global loads/stores of
+// sm_100; 16-byte vectors or scalars when a pointer is less aligned) with 64
+// bytes per operand in flight per thread, and a small functor supplies the
+// arithmetic.  The grid is a whole number of waves (SM count x resident CTAs),
+// each thread striding through the array so that consecutive threads touch
+// consecutive vectors.
 //
 // This file is compiled with -fmad=false: the reference rounds every multiply
 // and add separately (it is built without FMA contraction), and add, sub, mul,
@@ -24,6 +25,14 @@ template <> struct VecT<2> {
   using type = double2;
   static __device__ __forceinline__ double2 zero() { return make_double2(0.0, 0.0); }
 };
+// 32-byte vector: sm_100 has 256-bit global loads and stores (ld/st.global.v4.f64).
+struct __align__(32) double4v {
+  double x, y, z, w;
+};
+template <> struct VecT<4> {
+  using type = double4v;
+  static __device__ __forceinline__ double4v zero() { return double4v{0.0, 0.0, 0.0, 0.0}; }
+};
 template <> struct VecT<1> {
   using type = double;
   static __device__ __forceinline__ double zero() { return 0.0; }
@@ -34,6 +43,25 @@ __device__ __forceinline__ double lane(const double2 &v, int i) { return i == 0 
 __device__ __forceinline__ void set_lane(double &v, int, double x) { v = x; }
 __device__ __forceinline__ void set_lane(double2 &v, int i, double x) {
   if (i == 0) v.x = x; else v.y = x;
+}
+
+__device__ __forceinline__ double lane(const double4v &v, int i) {
+  return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w));
+}
+__device__ __forceinline__ void set_lane(double4v &v, int i, double x) {
+  if (i == 0) v.x = x; else if (i == 1) v.y = x; else if (i == 2) v.z = x; else v.w = x;
+}
+__device__ __forceinline__ double4v ld_stream(const double4v *p) {
+  double4v v;
+  asm volatile("ld.global.cs.v4.f64 {%0,%1,%2,%3}, [%4];"
+               : "=d"(v.x), "=d"(v.y), "=d"(v.z), "=d"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_stream(double4v *p, double4v v) {
+  asm volatile("st.global.cs.v4.f64 [%0], {%1,%2,%3,%4};" ::"l"(p), "d"(v.x), "d"(v.y), "d"(v.z),
+               "d"(v.w)
+               : "memory");
 }
 
 // Streaming loads/stores: every element is touched once, so keep it out of L1.
@@ -47,6 +75,7 @@ template <int VEC, class F>
 __global__ void __launch_bounds__(kEwThreads) map_kernel(F f, size_t n) {
   using V = typename VecT<VEC>::type;
   constexpr int NI = F::NI, NO = F::NO;
+  constexpr int kUnroll = VEC == 4 ? kEwUnroll / 2 : kEwUnroll;  // same bytes in flight per thread
   const size_t nvec = n / VEC;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -69,17 +98,17 @@ __global__ void __launch_bounds__(kEwThreads) map_kernel(F f, size_t n) {
 
   // Main loop: kEwUnroll independent vectors per thread; all loads are issued
   // before the first store so they overlap.
-  for (; i + (kEwUnroll - 1) * stride < nvec; i += kEwUnroll * stride) {
-    V v[kEwUnroll][NI > 0 ? NI : 1];
+  for (; i + (kUnroll - 1) * stride < nvec; i += kUnroll * stride) {
+    V v[kUnroll][NI > 0 ? NI : 1];
 #pragma unroll
-    for (int u = 0; u < kEwUnroll; u++) {
+    for (int u = 0; u < kUnroll; u++) {
 #pragma unroll
       for (int k = 0; k < NI; k++)
         v[u][k] = f.in[k] ? ld_stream(reinterpret_cast<const V *>(f.in[k]) + i + u * stride)
                           : VecT<VEC>::zero();
     }
 #pragma unroll
-    for (int u = 0; u < kEwUnroll; u++) process(v[u], i + u * stride);
+    for (int u = 0; u < kUnroll; u++) process(v[u], i + u * stride);
   }
   for (; i < nvec; i += stride) {
     V v[NI > 0 ? NI : 1];
@@ -88,29 +117,34 @@ __global__ void __launch_bounds__(kEwThreads) map_kernel(F f, size_t n) {
       v[k] = f.in[k] ? ld_stream(reinterpret_cast<const V *>(f.in[k]) + i) : VecT<VEC>::zero();
     process(v, i);
   }
-  // Odd tail element of the vector path.
-  if (VEC == 2 && (n & 1) && blockIdx.x == 0 && threadIdx.x == 0) {
+  // Tail elements of the vector paths (n not a multiple of VEC).
+  if (VEC > 1 && blockIdx.x == 0 && threadIdx.x < (unsigned)(n % VEC)) {
+    const size_t at = nvec * VEC + threadIdx.x;
     double si[NI > 0 ? NI : 1], so[NO];
 #pragma unroll
-    for (int k = 0; k < NI; k++) si[k] = f.in[k] ? f.in[k][n - 1] : 0.0;
+    for (int k = 0; k < NI; k++) si[k] = f.in[k] ? f.in[k][at] : 0.0;
     f.compute(si, so);
 #pragma unroll
     for (int k = 0; k < NO; k++)
-      if (f.out[k]) f.out[k][n - 1] = so[k];
+      if (f.out[k]) f.out[k][at] = so[k];
   }
 }
 
-template <class F> static bool all_aligned16(const F &f) {
+template <class F> static uintptr_t pointer_bits(const F &f) {
   uintptr_t bits = 0;
   for (int k = 0; k < F::NI; k++) bits |= reinterpret_cast<uintptr_t>(f.in[k]);
   for (int k = 0; k < F::NO; k++) bits |= reinterpret_cast<uintptr_t>(f.out[k]);
-  return (bits & 15) == 0;
+  return bits;
 }
 
 template <class F> static int launch_map(const F &f, size_t n, const char *name) {
   if (n == 0) return MG_OK;
   Context &c = ctx();
-  if (all_aligned16(f)) {
+  const uintptr_t bits = pointer_bits(f);
+  if ((bits & 31) == 0 && n >= 4096) {
+    unsigned grid = grid_for((n + 3) / 4, kEwThreads, kEwCtasPerSm);
+    map_kernel<4, F><<<grid, kEwThreads, 0, c.stream>>>(f, n);
+  } else if ((bits & 15) == 0) {
     unsigned grid = grid_for((n + 1) / 2, kEwThreads, kEwCtasPerSm);
     map_kernel<2, F><<<grid, kEwThreads, 0, c.stream>>>(f, n);
   } else {
