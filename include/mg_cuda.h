@@ -177,6 +177,10 @@ int mg_argmax_rows(const double *x, int *out, size_t M, size_t N);
 /* labels stored as doubles -> int class ids. */
 int mg_f64_to_i32(const double *src, int *dst, size_t n);
 
+/* avg_pool_2x2, src/nn.cpp:17-35, for a batch: x[batch,784] (28x28 images) ->
+ * out[batch,196]; each cell is ((a+b)+c)+d over its 2x2 window, divided by 4.0. */
+int mg_avg_pool_28(const double *x, double *out, size_t batch);
+
 /* ---- optimiser: src/nn.cpp:65-77 ----------------------------------------- */
 int mg_sgd_step(double *param, const double *grad, double lr, size_t n); /* p -= (lr*g) */
 

@@ -56,6 +56,9 @@ public:
   // parameter/gradient buffer) and uses that memory from now on.
   // `keepalive` owns that memory.
   void rehome(double *slice, std::shared_ptr<void> keepalive);
+  // Uses caller-owned device memory that already holds the values (a slice of a
+  // larger upload); `keepalive` owns that memory.
+  void adopt(double *slice, std::shared_ptr<void> keepalive);
   // True when the device buffer holds the current values (not logical zeros,
   // not superseded by a lent host view).
   bool device_current() const { return !zero_ && dev_valid_; }

@@ -136,6 +136,12 @@ def build_cpp_tests(force: bool = False, verbose: bool = False, reference: str =
         _run(common + [src, "-o", out] + link + ["-Wl,-rpath,$ORIGIN/../../../micrograd_b200/lib"],
              verbose)
     built.append(out)
+    out = os.path.join(bindir, "trainer_loop")
+    src = os.path.join(tests, "trainer_loop.cpp")
+    if force or _newer(out, [src, lib]):
+        _run(common + [src, "-o", out] + link + ["-Wl,-rpath,$ORIGIN/../../../micrograd_b200/lib"],
+             verbose)
+    built.append(out)
     ref_test = os.path.join(reference, "test", "tensor_test.cpp")
     if os.path.exists(ref_test):
         refdir = os.path.join(ROOT, "oracle", "_ref")
@@ -143,6 +149,14 @@ def build_cpp_tests(force: bool = False, verbose: bool = False, reference: str =
         out = os.path.join(refdir, "tensor_test_b200")
         if force or _newer(out, [ref_test, lib]):
             _run(common + [ref_test, "-o", out] + link +
+                 ["-Wl,-rpath,$ORIGIN/../../micrograd_b200/lib"], verbose)
+        built.append(out)
+        # the reference's trainer application, compiled unchanged (it needs MNIST
+        # files under ./data to do anything; building it proves the API surface)
+        ref_main = os.path.join(reference, "src", "main.cpp")
+        out = os.path.join(refdir, "main_b200")
+        if os.path.exists(ref_main) and (force or _newer(out, [ref_main, lib])):
+            _run([CXX, "-O2", "-std=c++20", f"-I{INCLUDE}", ref_main, "-o", out] + link +
                  ["-Wl,-rpath,$ORIGIN/../../micrograd_b200/lib"], verbose)
         built.append(out)
     return built

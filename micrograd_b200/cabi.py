@@ -74,6 +74,7 @@ SIGNATURES = {
                                       C.c_double, C.c_int]),
     "mg_argmax_rows": (C.c_int, [C.c_void_p, C.c_void_p, _sz, _sz]),
     "mg_f64_to_i32": (C.c_int, [C.c_void_p, C.c_void_p, _sz]),
+    "mg_avg_pool_28": (C.c_int, [C.c_void_p, C.c_void_p, _sz]),
     "mg_sgd_step": (C.c_int, [C.c_void_p, C.c_void_p, C.c_double, _sz]),
     "mg_event_create": (C.c_int, [_ip]),
     "mg_event_record": (C.c_int, [C.c_int]),

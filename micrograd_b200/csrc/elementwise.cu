@@ -325,6 +325,25 @@ row_scalar_bwd_kernel(const double *__restrict__ g, double *__restrict__ gx, siz
   }
 }
 
+// 2x2 mean pooling of 28x28 images stored as rows of 784 values -> rows of 196
+// (src/nn.cpp:17-35): ((a + b) + c) + d, then / 4.0, in the reference's order.
+__global__ void avg_pool_28_kernel(const double *__restrict__ x, double *__restrict__ out,
+                                   size_t batch) {
+  const size_t total = batch * 196;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const size_t b = i / 196, cell = i % 196;
+    const size_t py = cell / 14, px = cell % 14;
+    const double *img = x + b * 784 + (py * 2) * 28 + px * 2;
+    double sum = 0.0;
+    sum += img[0];
+    sum += img[1];
+    sum += img[28];
+    sum += img[29];
+    out[i] = sum / 4.0;
+  }
+}
+
 __global__ void f64_to_i32_kernel(const double *__restrict__ src, int *__restrict__ dst, size_t n) {
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
@@ -512,6 +531,15 @@ int mg_sum_lastaxis_bwd(const double *g, double *gx, size_t M, size_t N, int fla
     row_scalar_bwd_kernel<1><<<grid, kEwThreads, 0, c.stream>>>(g, gx, M, N, acc);
   }
   MG_LAUNCH_CHECK("sum_lastaxis_bwd");
+  return MG_OK;
+}
+
+int mg_avg_pool_28(const double *x, double *out, size_t batch) {
+  MG_ENSURE_INIT();
+  if (batch == 0) return MG_OK;
+  if (!x || !out) return fail(MG_ERR_INVALID, "mg_avg_pool_28: null pointer");
+  avg_pool_28_kernel<<<grid_for(batch * 196, 256, 8), 256, 0, ctx().stream>>>(x, out, batch);
+  MG_LAUNCH_CHECK("avg_pool_28");
   return MG_OK;
 }
 

@@ -5,21 +5,19 @@
 #include <iomanip>
 #include <sstream>
 #include <unordered_set>
+#include <utility>
 #include <vector>
 
 std::string to_dot(const std::shared_ptr<Tensor> &tensor) {
   std::ostringstream out;
-  out << "digraph {\n  rankdir=LR;\n";
+  out << "digraph {\n";
+  out << "  rankdir=LR;\n";
 
+  // Same text, line for line, as the reference's recursive walk: a node, its op
+  // box, then per child the edge followed by that child's subtree.  Done with
+  // an explicit stack of (node, next child) frames.
   std::unordered_set<Tensor *> seen;
-  std::vector<Tensor *> work{tensor.get()};
-  // Depth-first, children in order, like the reference's recursive walk.
-  while (!work.empty()) {
-    Tensor *node = work.back();
-    work.pop_back();
-    if (!seen.insert(node).second) {
-      continue;
-    }
+  auto emit_node = [&](Tensor *node) {
     out << "  \"" << node << "\" [label=\"data: " << node->data_.peek(0);
     if (node->size() > 1) {
       out << "...";
@@ -29,16 +27,28 @@ std::string to_dot(const std::shared_ptr<Tensor> &tensor) {
       out << "...";
     }
     out << "\", shape=record];\n";
-    if (node->op_.empty()) {
+    if (!node->op_.empty()) {
+      out << "  \"" << node << "_op\" [label=\"" << node->op_ << "\"];\n";
+      out << "  \"" << node << "_op\" -> \"" << node << "\";\n";
+    }
+  };
+  std::vector<std::pair<Tensor *, size_t>> stack;
+  seen.insert(tensor.get());
+  emit_node(tensor.get());
+  stack.emplace_back(tensor.get(), 0);
+  while (!stack.empty()) {
+    Tensor *node = stack.back().first;
+    size_t &next = stack.back().second;
+    if (node->op_.empty() || next >= node->children_.size()) {
+      stack.pop_back();
       continue;
     }
-    out << "  \"" << node << "_op\" [label=\"" << node->op_ << "\"];\n";
-    out << "  \"" << node << "_op\" -> \"" << node << "\";\n";
-    for (auto &child : node->children_) {
-      out << "  \"" << child.get() << "\" -> \"" << node << "_op\";\n";
-    }
-    for (auto it = node->children_.rbegin(); it != node->children_.rend(); ++it) {
-      work.push_back(it->get());
+    Tensor *child = node->children_[next].get();
+    next++;
+    out << "  \"" << child << "\" -> \"" << node << "_op\";\n";
+    if (seen.insert(child).second) {
+      emit_node(child);
+      stack.emplace_back(child, 0);
     }
   }
   out << "}\n";

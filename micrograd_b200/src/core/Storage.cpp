@@ -8,6 +8,10 @@
 
 namespace micrograd::detail {
 
+namespace {
+constexpr size_t kKeepHostElems = 4096;
+}
+
 void check(int rc, const char *what) {
   if (rc != MG_OK) {
     throw std::runtime_error(std::string(what) + ": " + mg_last_error());
@@ -47,7 +51,14 @@ void Storage::init_from_host(std::vector<double> &&values) {
   check(mg_upload(dev_, values.data(), size_), "upload");
   zero_ = false;
   dev_valid_ = true;
-  host_valid_ = false;
+  // Small tensors (labels, scalars, single samples) keep their host copy, so
+  // reading them back through at()/data() needs no device round trip.
+  if (size_ <= kKeepHostElems) {
+    host_ = std::move(values);
+    host_valid_ = true;
+  } else {
+    host_valid_ = false;
+  }
 }
 
 void Storage::settle_upload() {
@@ -198,6 +209,20 @@ void Storage::rehome(double *slice, std::shared_ptr<void> keepalive) {
   dev_ = slice;
   owns_dev_ = false;
   keepalive_ = std::move(keepalive);
+}
+
+void Storage::adopt(double *slice, std::shared_ptr<void> keepalive) {
+  settle_upload();
+  if (dev_ && owns_dev_) {
+    check(mg_free(dev_), "free");
+  }
+  dev_ = slice;
+  owns_dev_ = false;
+  keepalive_ = std::move(keepalive);
+  zero_ = false;
+  dev_valid_ = true;
+  host_valid_ = false;
+  write_stamp_++;
 }
 
 DeviceInts::DeviceInts(const int *host_values, size_t n) : n_(n) {

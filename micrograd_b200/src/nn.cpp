@@ -9,40 +9,11 @@
 #include <random>
 #include <stdexcept>
 
+#include "internal.h"
 #include "mg_cuda.h"
 
 using micrograd::detail::check;
 using micrograd::detail::DeviceInts;
-
-namespace micrograd::detail {
-// The one friend of Tensor outside the class: lets the free functions and
-// classes of this file reach storage and graph fields.
-struct TensorAccess {
-  static Storage &data(Tensor &t) { return t.data_; }
-  static Storage &grad(Tensor &t) { return t.grad_; }
-  static std::vector<std::shared_ptr<Tensor>> &children(Tensor &t) { return t.children_; }
-  static std::function<void(Tensor &)> &backward_fn(Tensor &t) { return t.backward_fn_; }
-  static std::function<void(Tensor &)> &hook(Tensor &t) { return t.grad_ready_hook_; }
-  static bool requires_grad(const Tensor &t) { return t.requires_grad_; }
-  static void mark_relu_output(Tensor &t) { t.relu_output_ = true; }
-  static bool is_relu_output(const Tensor &t) { return t.relu_output_; }
-  // True if the gradient buffer holds only values that already carry the ReLU
-  // mask (or nothing at all).
-  static bool grad_fully_masked(Tensor &t) {
-    return t.grad_.is_zero() || (t.grad_premasked_ && t.grad_.device_current() &&
-                                 t.grad_.write_stamp() == t.grad_premasked_stamp_);
-  }
-  static void commit_premask(Tensor &t, bool fully_masked) {
-    t.grad_premasked_ = fully_masked;
-    t.grad_premasked_stamp_ = t.grad_.write_stamp();
-  }
-  static std::shared_ptr<Tensor> make_result(Tensor &owner, std::vector<size_t> shape,
-                                             std::string label,
-                                             std::vector<std::shared_ptr<Tensor>> children) {
-    return owner.make_result(std::move(shape), std::move(label), std::move(children));
-  }
-};
-}  // namespace micrograd::detail
 
 using Access = micrograd::detail::TensorAccess;
 
@@ -54,23 +25,23 @@ std::shared_ptr<Tensor> mse_loss(const std::shared_ptr<Tensor> &prediction,
   return squared->sum()->div(static_cast<double>(prediction->size()));
 }
 
-// 28x28 -> 14x14 mean pooling of one image row vector; like the reference
-// (nn.cpp:17-35) it returns a fresh leaf, i.e. it is not differentiable.
+// 28x28 -> 14x14 mean pooling of image row vectors, on the device; like the
+// reference (nn.cpp:17-35) it returns a fresh leaf, i.e. it is not
+// differentiable.  The reference handles one [1,784] image; any [B,784] batch is
+// accepted here (the reference reads row 0 only, which is what B = 1 gives).
 std::shared_ptr<Tensor> avg_pool_2x2(const std::shared_ptr<Tensor> &input) {
-  const Tensor &image = *input;
-  std::vector<double> pooled(14 * 14);
-  for (size_t py = 0; py < 14; py++) {
-    for (size_t px = 0; px < 14; px++) {
-      double total = 0.0;
-      for (size_t dy = 0; dy < 2; dy++) {
-        for (size_t dx = 0; dx < 2; dx++) {
-          total += image.at({0, (py * 2 + dy) * 28 + (px * 2 + dx)});
-        }
-      }
-      pooled[py * 14 + px] = total / 4.0;
-    }
+  const auto &shape = input->shape();
+  size_t batch = 1;
+  if (shape.size() == 2 && shape[1] == 784) {
+    batch = shape[0];
+  } else if (input->size() < 784) {
+    throw std::invalid_argument("avg_pool_2x2 needs 784 values per image");
   }
-  return std::make_shared<Tensor>(std::vector<size_t>{1, 196}, std::move(pooled));
+  auto pooled = std::make_shared<Tensor>(std::vector<size_t>{batch, 196});
+  check(mg_avg_pool_28(Access::data(*input).device_read(), Access::data(*pooled).device_overwrite(),
+                       batch),
+        "avg_pool_2x2");
+  return pooled;
 }
 
 // Weights [in, out] ~ U(-0.1, 0.1) from a non-deterministic seed, bias [1, out]

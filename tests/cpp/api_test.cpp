@@ -4,6 +4,8 @@
 #include <gtest/gtest.h>
 
 #include <cmath>
+#include <cstdio>
+#include <fstream>
 #include <memory>
 #include <stdexcept>
 #include <vector>
@@ -11,6 +13,7 @@
 #include "mg_cuda.h"
 #include "micrograd/Tensor.h"
 #include "micrograd/Utils.h"
+#include "micrograd/mnist.h"
 #include "micrograd/nn.h"
 
 using TensorPtr = std::shared_ptr<Tensor>;
@@ -127,4 +130,45 @@ TEST(ApiTest, ToDotMentionsOps) {
   EXPECT_TRUE(dot.find("digraph {") == 0);
   EXPECT_TRUE(dot.find("* 3.00") != std::string::npos);
   EXPECT_EQ(format_scalar("/", 4.0), std::string("/ 4.00"));
+}
+
+// IDX reader: same per-sample tensors as the reference's load_mnist (one [1,784]
+// image scaled by 1/255 and a one-hot [1,10] label), plus the batched form.
+TEST(ApiTest, LoadMnistFromIdxFiles) {
+  const char *img_path = "/tmp/mg_b200_test-images-idx3-ubyte";
+  const char *lbl_path = "/tmp/mg_b200_test-labels-idx1-ubyte";
+  const int count = 5;
+  {
+    std::ofstream img(img_path, std::ios::binary), lbl(lbl_path, std::ios::binary);
+    std::vector<char> header(16, 0);
+    img.write(header.data(), 16);
+    lbl.write(header.data(), 8);
+    for (int i = 0; i < count; i++) {
+      for (int j = 0; j < 784; j++) {
+        unsigned char px = static_cast<unsigned char>((i * 37 + j * 11) % 256);
+        img.write(reinterpret_cast<char *>(&px), 1);
+      }
+      unsigned char label = static_cast<unsigned char>((i * 3) % 10);
+      lbl.write(reinterpret_cast<char *>(&label), 1);
+    }
+  }
+  MNISTData data = load_mnist(img_path, lbl_path, count);
+  ASSERT_EQ(data.images.size(), static_cast<size_t>(count));
+  ASSERT_EQ(data.labels.size(), static_cast<size_t>(count));
+  for (int i = 0; i < count; i++) {
+    EXPECT_EQ(data.images[i]->shape().size(), static_cast<size_t>(2));
+    EXPECT_EQ(data.images[i]->size(), static_cast<size_t>(784));
+    EXPECT_EQ(data.images[i]->at({0, 5}), ((i * 37 + 5 * 11) % 256) / 255.0);
+    EXPECT_EQ(data.labels[i]->at({0, static_cast<size_t>((i * 3) % 10)}), 1.0);
+    EXPECT_EQ(data.labels[i]->sum()->data()[0], 1.0);
+  }
+  // the per-sample views feed the ops like any other tensor
+  auto pooled = avg_pool_2x2(data.images[2]);
+  EXPECT_EQ(pooled->size(), static_cast<size_t>(196));
+  MNISTBatch batch = load_mnist_batched(img_path, lbl_path, count);
+  EXPECT_EQ(batch.images->shape()[0], static_cast<size_t>(count));
+  EXPECT_EQ(batch.labels->at({4}), 2.0);
+  EXPECT_EQ(batch.images->at({3, 7}), data.images[3]->at({0, 7}));
+  std::remove(img_path);
+  std::remove(lbl_path);
 }

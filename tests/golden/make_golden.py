@@ -133,6 +133,53 @@ def mlp_case(rng):
     return out
 
 
+REFERENCE_MODEL = "/root/reference/models/mnist.bin"
+
+
+def trainer_cases(api, rng):
+    """The reference trainer's per-sample loop (src/main.cpp:20-46) on synthetic
+    images: avg_pool -> Linear(196,100) -> relu -> Linear(100,10) -> mse_loss,
+    host argmax, zero_grad, backward, SGD step lr 0.01 — two epochs over 24
+    samples, starting from the weights of the reference's models/mnist.bin.
+    Also plain inference with those weights on 64 images."""
+    l1, l2 = api.Linear(196, 100), api.Linear(100, 10)
+    api.load_model(REFERENCE_MODEL, l1, l2)
+    out = {"W1": l1.weights().data().reshape(196, 100), "b1": l1.bias().data(),
+           "W2": l2.weights().data().reshape(100, 10), "b2": l2.bias().data()}
+    images = rng.random((64, 784))
+    logits = []
+    for i in range(64):
+        x = api.Tensor([1, 784], images[i])
+        logits.append(l2.forward(l1.forward(api.avg_pool_2x2(x)).relu()).data())
+    out["infer_images"] = images
+    out["infer_logits"] = np.array(logits)
+    train_images = rng.random((24, 784))
+    train_labels = rng.integers(0, 10, 24)
+    opt = api.SGD([l1.weights(), l1.bias(), l2.weights(), l2.bias()], 0.01)
+    losses, preds = [], []
+    for epoch in range(2):
+        for i in range(24):
+            onehot = np.zeros(10)
+            onehot[train_labels[i]] = 1.0
+            x = l1.forward(api.avg_pool_2x2(api.Tensor([1, 784], train_images[i]))).relu()
+            o = l2.forward(x)
+            loss = api.mse_loss(o, api.Tensor([1, 10], onehot))
+            pred = 0
+            for j in range(10):
+                if o.at([0, j]) > o.at([0, pred]):
+                    pred = j
+            preds.append(pred)
+            opt.zero_grad()
+            loss.backward()
+            opt.step()
+            losses.append(loss.at([0]))
+    out.update(train_images=train_images, train_labels=train_labels, losses=np.array(losses),
+               preds=np.array(preds), W1_final=l1.weights().data().reshape(196, 100),
+               b1_final=l1.bias().data(), W2_final=l2.weights().data().reshape(100, 10),
+               b2_final=l2.bias().data())
+    return out
+
+
 def main():
     api = oracle.ref_true()
     rng = np.random.default_rng(20240611)
@@ -140,6 +187,7 @@ def main():
     np.savez(os.path.join(HERE, "matmul_sum.npz"), **matmul_cases(api, rng))
     np.savez(os.path.join(HERE, "mse.npz"), **mse_case(api, rng))
     np.savez(os.path.join(HERE, "mlp_c1.npz"), **mlp_case(rng))
+    np.savez(os.path.join(HERE, "trainer_mnist_bin.npz"), **trainer_cases(api, rng))
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
