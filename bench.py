@@ -401,7 +401,7 @@ def gemm_roofline(abi, K, rows):
             "traffic_source": "ncu capture at batch 32768, scaled by rows"}
 
 
-def metric_sweeps(abi, K):
+def metric_sweeps(abi, K, small=False):
     """The other two parts of the BASELINE metric, measured on one GPU with events:
     DGEMM TFLOP/s (forward C = A.B; BASELINE config 3 shapes) and elementwise /
     reduction GB/s (BASELINE config 2 ops at 2^24 and 2^28 elements, algorithmic
@@ -422,14 +422,15 @@ def metric_sweeps(abi, K):
         return abi.timed_ms(fn, reps) / reps
 
     out = {"dgemm_tflops": {}, "elementwise_gbs": {}}
-    for tag, (m, n, k), reps in (("1024^3", (1024, 1024, 1024), 20), ("4096^3", (4096, 4096, 4096), 3),
-                                 ("8192^3", (8192, 8192, 8192), 2),
-                                 ("65536x784.784x1024", (65536, 1024, 784), 3)):
+    gemm_cases = (("1024^3", (1024, 1024, 1024), 20), ("4096^3", (4096, 4096, 4096), 3),
+                  ("8192^3", (8192, 8192, 8192), 2), ("65536x784.784x1024", (65536, 1024, 784), 3))
+    # small=True: the 2^24 / 2^26 elementwise cases only (what a profiler capture needs)
+    for tag, (m, n, k), reps in (() if small else gemm_cases):
         a, b, c = filled(m * k), filled(k * n), abi.empty(m * n)
         ms = timed(lambda: abi.mg_gemm_nn(a.ptr, b.ptr, c.ptr, m, n, k, 0, K.EPI_NONE, None), reps)
         out["dgemm_tflops"][tag] = round(2.0 * m * n * k / ms / 1e9, 2)
         del a, b, c
-    for log2n in (24, 28):
+    for log2n in ((24, 26) if small else (24, 28)):
         n = 1 << log2n
         a, b, g, o = filled(n), filled(n), filled(n), abi.empty(n)
         side = 1 << (log2n // 2)
@@ -525,11 +526,19 @@ def main():
                     help="skip the DGEMM / elementwise sweeps that fill the `sweeps` key")
     ap.add_argument("--sync-each-step", action="store_true",
                     help="diagnostic: host waits for the device after every step")
+    ap.add_argument("--sweeps-only", action="store_true",
+                    help="run only the DGEMM / elementwise sweeps on one GPU (for profiler captures)")
     ap.add_argument("--value-only", action="store_true",
                     help="run only the device-resident leg (for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.sweeps_only:
+        import micrograd_b200
+        from micrograd_b200 import cabi as K
+        abi = micrograd_b200.load_abi()
+        abi.mg_init(0)
+        print(json.dumps({"sweeps": metric_sweeps(abi, K, small=True)}), flush=True)
     else:
         if args.warmup < 3:
             args.warmup = 3
