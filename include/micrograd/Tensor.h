@@ -71,7 +71,7 @@ public:
   // add(b) also accepts a row vector b of shape [1,N] or [N] against [M,N]
   // (M > 1), broadcasting it over the rows; the reference throws for that case.
   std::shared_ptr<Tensor> exp();
-  // Sum over one axis of a 2-D tensor; only the last axis is implemented.
+  // Sum over one axis (0, 1 or -1) of a 2-D tensor.
   std::shared_ptr<Tensor> sum(int axis);
   // A tensor that does not require a gradient is skipped by backward(): no
   // gradient buffer is allocated for it and the product that would fill it is

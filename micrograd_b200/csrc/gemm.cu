@@ -2,9 +2,12 @@
 // gradient products dA += G.B^T (:44-50) and dB += A^T.G (:52-58).
 //
 // Main kernel: FP64 tensor-core (DMMA, mma.sync ... f64) tiles fed by TMA.
-//   - CTA tile 128 x 128 x 16, eight consumer warps (2 x 4, each 64 x 32) and one
-//     producer warp group (registers re-split with setmaxnreg); a ring of 32 KB stages filled by cp.async.bulk.tensor and
-//     handed over through full/empty mbarriers.
+//   - Eight consumer warps and one producer warp group per CTA (registers re-split
+//     with setmaxnreg); a ring of stages filled by cp.async.bulk.tensor and handed
+//     over through full/empty mbarriers.  Tile configurations (TileCfg): 128 x 128
+//     (2 x 4 warps of 64 x 32) for the compute-bound shapes, 128 x 64 when that
+//     fills the last wave of CTAs better, 128 x 32 for outputs at most 32 columns
+//     wide, 112 x 128 for row counts that are multiples of 112 but not of 128.
 //   - Operands land in shared memory in the 128-byte swizzle.  With the k index
 //     of a 16-deep slab permuted (the same permutation for A and B, so the sum is
 //     unchanged) every fragment load is free of bank conflicts: a thread reads
@@ -14,11 +17,14 @@
 //        mn-contiguous tile [16-col group][k][16 cols] : 8-byte loads
 //   - The accumulators stay in registers (FP64 MMA has no TMEM form); the
 //     epilogue adds the bias, applies ReLU or the ReLU mask, and stores or
-//     accumulates 16 bytes per thread per row.
+//     accumulates 16 bytes per thread per row, all loads before the stores.
 //   - When the output has too few tiles to fill 148 SMs (weight gradients: the
-//     contraction runs over the batch), the contraction is split across
-//     the grid and a second kernel folds the partial tiles in index order, so
-//     the result is still reproducible.
+//     contraction runs over the batch), the contraction is split across the grid
+//     and a second kernel folds the partial tiles in index order, so the result
+//     is still reproducible.
+//   - Short work items run as a persistent grid (one CTA per SM looping over
+//     items, the producer prefetching across items); long ones as one item per
+//     CTA under the hardware scheduler.
 // Fallback kernel: a plain shared-memory tiled FMA kernel with full bounds
 // checks for shapes the TMA path cannot take (odd row lengths, unaligned
 // bases) and for tiny problems.
@@ -580,13 +586,9 @@ struct DmmaLaunch {
   int grouped_ab;  // bit 0 / bit 1: operand A / B uses the grouped 3-D tensor map
 };
 
-// A rectangle of tiles: rows [m0, m0 + rows), columns [n0, n0 + cols).
-struct TileRegion {
-  int m0, n0, rows, cols;
-};
 
 template <bool AK, bool BK_, int SHAPE, bool EDGE, class Cfg, bool PERSISTENT>
-static int launch_dmma_variant(const DmmaLaunch &L, const TileRegion &R) {
+static int launch_dmma_variant(const DmmaLaunch &L) {
   static bool configured = false;
   auto kernel = dmma_gemm_kernel<AK, BK_, SHAPE, EDGE, Cfg, PERSISTENT>;
   if (!configured) {
@@ -595,16 +597,16 @@ static int launch_dmma_variant(const DmmaLaunch &L, const TileRegion &R) {
     configured = true;
   }
   Context &c = ctx();
-  const int tiles = R.rows * R.cols;
+  const int tiles = L.tiles_m * L.tiles_n;
   // bottom row of tiles less than half full -> its tiles are "light"
-  const int light = ((L.M % Cfg::BM) != 0 && (L.M % Cfg::BM) * 2 < Cfg::BM && R.rows > 1) ? R.cols : 0;
+  const int light = ((L.M % Cfg::BM) != 0 && (L.M % Cfg::BM) * 2 < Cfg::BM && L.tiles_m > 1) ? L.tiles_n : 0;
   const int items = tiles * L.splits;
   // Long items (many k-tiles) are left to the hardware scheduler, one item per
   // CTA: it balances them dynamically.  Short items (skinny or shallow problems)
   // run as a persistent grid, where the cross-item prefetch hides the pipeline
   // fill that would otherwise dominate them.
   dim3 grid((unsigned)((PERSISTENT && items > c.sm_count) ? c.sm_count : items), 1, 1);
-  kernel<<<grid, kGemmThreads, Cfg::SMEM_BYTES, c.stream>>>(L.ma, L.mb, L.ep, L.M, L.N, L.K, R.cols,
+  kernel<<<grid, kGemmThreads, Cfg::SMEM_BYTES, c.stream>>>(L.ma, L.mb, L.ep, L.M, L.N, L.K, L.tiles_n,
                                                              tiles - light, light, L.splits,
                                                              L.kt_per_split, L.grouped_ab, items,
                                                              c.kernel_status);
@@ -613,28 +615,26 @@ static int launch_dmma_variant(const DmmaLaunch &L, const TileRegion &R) {
 }
 
 template <bool AK, bool BK_, int SHAPE, bool EDGE, class Cfg>
-static int launch_dmma_kernel(const DmmaLaunch &L, const TileRegion &R) {
-  if (R.rows <= 0 || R.cols <= 0) return MG_OK;
+static int launch_dmma_kernel(const DmmaLaunch &L) {
   static const int persist_mode = [] {
     const char *v = std::getenv("MG_GEMM_PERSIST");  // diagnostic: 0 never, 1 always
     return v && *v ? std::atoi(v) : -1;
   }();
   bool persistent = (L.kt_per_split < 32 || Cfg::BN <= 32) &&
-                    R.rows * R.cols * L.splits > ctx().sm_count;
+                    L.tiles_m * L.tiles_n * L.splits > ctx().sm_count;
   if (persist_mode == 0) persistent = false;
   if (persist_mode == 1) persistent = true;
-  if (persistent) return launch_dmma_variant<AK, BK_, SHAPE, EDGE, Cfg, true>(L, R);
-  return launch_dmma_variant<AK, BK_, SHAPE, EDGE, Cfg, false>(L, R);
+  if (persistent) return launch_dmma_variant<AK, BK_, SHAPE, EDGE, Cfg, true>(L);
+  return launch_dmma_variant<AK, BK_, SHAPE, EDGE, Cfg, false>(L);
 }
 
 // One launch over all tiles; problems with a ragged border use the instantiation
 // that can skip out-of-range sub-tiles.
 template <bool AK, bool BK_, int SHAPE, class Cfg>
-static int launch_regions(const DmmaLaunch &L) {
-  const TileRegion all{0, 0, L.tiles_m, L.tiles_n};
+static int launch_tiles(const DmmaLaunch &L) {
   if ((L.M % Cfg::BM) != 0 || (L.N % Cfg::BN) != 0)
-    return launch_dmma_kernel<AK, BK_, SHAPE, true, Cfg>(L, all);
-  return launch_dmma_kernel<AK, BK_, SHAPE, false, Cfg>(L, all);
+    return launch_dmma_kernel<AK, BK_, SHAPE, true, Cfg>(L);
+  return launch_dmma_kernel<AK, BK_, SHAPE, false, Cfg>(L);
 }
 
 enum TileChoice { kTileMain = 0, kTileSkinny = 1, kTileHalf = 2, kTileRows112 = 3 };
@@ -643,14 +643,14 @@ template <bool AK, bool BK_>
 static int launch_layout(int shape, int tile, const DmmaLaunch &L) {
   // The narrow and half-width configurations exist for the default mma shape only.
   if (tile == kTileSkinny)
-    return launch_dmma_kernel<AK, BK_, 2, true, SkinnyCfg>(L, TileRegion{0, 0, L.tiles_m, L.tiles_n});
-  if (tile == kTileHalf) return launch_regions<AK, BK_, 2, HalfCfg>(L);
-  if (tile == kTileRows112) return launch_regions<AK, BK_, 2, Rows112Cfg>(L);
+    return launch_dmma_kernel<AK, BK_, 2, true, SkinnyCfg>(L);
+  if (tile == kTileHalf) return launch_tiles<AK, BK_, 2, HalfCfg>(L);
+  if (tile == kTileRows112) return launch_tiles<AK, BK_, 2, Rows112Cfg>(L);
   switch (shape) {
-    case 0: return launch_regions<AK, BK_, 0, MainCfg>(L);
-    case 1: return launch_regions<AK, BK_, 1, MainCfg>(L);
-    case 3: return launch_regions<AK, BK_, 3, MainCfg>(L);
-    default: return launch_regions<AK, BK_, 2, MainCfg>(L);
+    case 0: return launch_tiles<AK, BK_, 0, MainCfg>(L);
+    case 1: return launch_tiles<AK, BK_, 1, MainCfg>(L);
+    case 3: return launch_tiles<AK, BK_, 3, MainCfg>(L);
+    default: return launch_tiles<AK, BK_, 2, MainCfg>(L);
   }
 }
 
