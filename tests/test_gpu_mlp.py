@@ -128,3 +128,47 @@ def test_from_host_upload_matches_constructor(api):
     b = api.from_host([64, 784], X.ctypes.data)
     api.synchronize()
     assert np.array_equal(a.data(), b.data())
+
+
+def _train_both(api, fast, sizes, batch, steps, lr=0.01, seed=0):
+    rng = np.random.default_rng(seed)
+    params = [(rng.standard_normal((i, o)) / np.sqrt(i), np.zeros(o)) for i, o in zip(sizes[:-1], sizes[1:])]
+    X, y = rng.random((batch, sizes[0])), rng.integers(0, 10, batch).astype(np.int32)
+    layers = build_mlp(api, params)
+    opt = api.SGD([t for lin in layers for t in (lin.weights(), lin.bias())], lr)
+    opt.enable_allreduce()
+    ref = [(W.copy(), b.copy()) for W, b in params]
+    x = api.Tensor([batch, sizes[0]], X)
+    x.set_requires_grad(False)
+    labels = api.Tensor([batch], y.astype(np.float64))
+    got, want = [], []
+    for _ in range(steps):
+        loss = api.softmax_cross_entropy(forward(api, layers, x, True), labels)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        got.append(loss)
+        want.append(fast.mlp_train_step(ref, X, y, lr)[0])
+    got = np.array([t.data()[0] for t in got])
+    return got, np.array(want), layers, ref
+
+
+def test_hundred_steps_of_config4_architecture_at_reduced_batch(api, fast):
+    """784-1024-1024-10, 100 SGD steps (BASELINE config 4's step count) at batch 256:
+    the whole loss curve and the final parameters against the oracle."""
+    got, want, layers, ref = _train_both(api, fast, [784, 1024, 1024, 10], 256, 100)
+    assert np.max(np.abs(got - want) / np.abs(want)) <= 1e-9
+    assert want[-1] < want[0]                                  # it does learn its batch
+    for lin, (W, b) in zip(layers, ref):
+        assert norm_err(lin.weights().data(), W.reshape(-1)) <= 1e-9
+        assert norm_err(lin.bias().data(), b) <= 1e-9
+
+
+def test_two_full_batch_steps_of_config4(api, fast):
+    """BASELINE config 4 at its full size (global batch 65536): two SGD steps against
+    the multi-threaded order-preserving oracle (about half a minute of host time)."""
+    got, want, layers, ref = _train_both(api, fast, [784, 1024, 1024, 10], 65536, 2)
+    assert np.max(np.abs(got - want) / np.abs(want)) <= 1e-10
+    for lin, (W, b) in zip(layers, ref):
+        assert norm_err(lin.weights().data(), W.reshape(-1)) <= 1e-10
+        assert norm_err(lin.bias().data(), b) <= 1e-10
