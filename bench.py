@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Benchmark of the fp64 MLP training hot path (BASELINE config 4).
+"""Benchmark of the fp64 MLP training hot path (benchmark config 4).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
@@ -339,7 +339,7 @@ def run_product(args):
         "warmup": args.warmup, "ms_per_step": ms_per_step, "ms_per_step_spread": step_spread,
         "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-        "config": {"workload": "MLP 784-1024-1024-10 fp64 train step (BASELINE config 4)",
+        "config": {"workload": "MLP 784-1024-1024-10 fp64 train step (benchmark config 4)",
                    "global_batch": batch, "rows_per_gpu": rows, "lr": LR, "parallelism": f"dp{world}",
                    "input_grad": False, "l2": "per-step working set (activations+gradients > 1 GB "
                    "at N=1, > 300 MB at N=8) exceeds the 126 MB L2"},
@@ -402,9 +402,9 @@ def gemm_roofline(abi, K, rows):
 
 
 def metric_sweeps(abi, K, small=False):
-    """The other two parts of the BASELINE metric, measured on one GPU with events:
-    DGEMM TFLOP/s (forward C = A.B; BASELINE config 3 shapes) and elementwise /
-    reduction GB/s (BASELINE config 2 ops at 2^24 and 2^28 elements, algorithmic
+    """The other two parts of the headline metric, measured on one GPU with events:
+    DGEMM TFLOP/s (forward C = A.B; benchmark config 3 shapes) and elementwise /
+    reduction GB/s (benchmark config 2 ops at 2^24 and 2^28 elements, algorithmic
     bytes per element: binary forward 24, unary forward 16, sums 8).  Arrays are
     far larger than L2 at both sizes."""
     rng = np.random.default_rng(11)
@@ -504,7 +504,7 @@ def run_reference(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": base["ms_per_step"], "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-        "config": {"workload": "MLP 784-1024-1024-10 fp64 train step (BASELINE config 4)",
+        "config": {"workload": "MLP 784-1024-1024-10 fp64 train step (benchmark config 4)",
                    "global_batch": args.batch, "rows_per_step_sample": base["rows"], "lr": LR,
                    "parallelism": "cpu, 1 thread"},
         "cpu_baseline": base,

@@ -114,7 +114,12 @@ def build_tensor(force: bool = False, verbose: bool = False) -> str:
     return out
 
 
-def build_cpp_tests(force: bool = False, verbose: bool = False, reference: str = "/root/reference"):
+def reference_dir() -> str:
+    """The reference checkout: $MICROGRAD_REFERENCE, else a sibling of this repository."""
+    return os.environ.get("MICROGRAD_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference")
+
+
+def build_cpp_tests(force: bool = False, verbose: bool = False, reference: str | None = None):
     """C++ test binaries (run by tests/test_gpu_cpp.py on a GPU machine):
 
     tests/cpp/bin/api_test         this repository's own C++ API tests
@@ -142,6 +147,7 @@ def build_cpp_tests(force: bool = False, verbose: bool = False, reference: str =
         _run(common + [src, "-o", out] + link + ["-Wl,-rpath,$ORIGIN/../../../micrograd_b200/lib"],
              verbose)
     built.append(out)
+    reference = reference or reference_dir()
     ref_test = os.path.join(reference, "test", "tensor_test.cpp")
     if os.path.exists(ref_test):
         refdir = os.path.join(ROOT, "oracle", "_ref")

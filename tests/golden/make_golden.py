@@ -114,7 +114,7 @@ def mse_case(api, rng):
 
 
 def mlp_case(rng):
-    """BASELINE config 1: 784-128-64-10, batch 32, one SGD step, lr 0.01."""
+    """Benchmark config 1: 784-128-64-10, batch 32, one SGD step, lr 0.01."""
     sizes = [784, 128, 64, 10]
     batch = 32
     params = [(rng.standard_normal((i, o)) / np.sqrt(i), np.zeros(o))
@@ -133,7 +133,9 @@ def mlp_case(rng):
     return out
 
 
-REFERENCE_MODEL = "/root/reference/models/mnist.bin"
+REFERENCE_MODEL = os.path.join(
+    os.environ.get("MICROGRAD_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference"),
+    "models", "mnist.bin")
 
 
 def trainer_cases(api, rng):

@@ -1,7 +1,7 @@
 """GPU parity: elementwise forward/backward kernels, through the device C ABI,
 against the CPU oracle on identical seeded inputs.
 
-Tolerances (BASELINE north_star): rel err <= 1e-12 for elementwise ops.  add,
+Tolerances (the stated parity bar): rel err <= 1e-12 for elementwise ops.  add,
 sub, mul, div, relu, the scalar forms, their gradients, fill and the SGD update
 use only correctly rounded IEEE operations with no FMA contraction on either
 side, so for those the comparison is bit-exact.
@@ -175,7 +175,7 @@ def test_add_row_forward(abi, fast, M, N):
 
 
 def test_elementwise_full_size_properties(abi):
-    """2^24 elements (a BASELINE sweep size): linearity and idempotence properties
+    """2^24 elements (a benchmark sweep size): linearity and idempotence properties
     that need no CPU pass over the data: (a+b)-b == a within one rounding,
     relu(relu(x)) == relu(x) exactly, and x*1 == x exactly."""
     n = 1 << 24

@@ -1,4 +1,4 @@
-"""GPU: BASELINE's full sizes, checked through size-independent properties (the
+"""GPU: the benchmark's full sizes, checked through size-independent properties (the
 CPU oracle would need minutes to hours at these sizes), plus spot checks of a
 few rows against the oracle.
 

@@ -1,7 +1,7 @@
 """GPU parity: matmul forward and both gradient products through the device C
 ABI (mg_gemm_nn / _nt / _tn) against the CPU oracle.
 
-Tolerance (BASELINE north_star): rel err <= 1e-10 for matmul.  Element (i,j) is
+Tolerance (the stated parity bar): rel err <= 1e-10 for matmul.  Element (i,j) is
 compared against the natural bound of its dot product, sum_p |a_ip||b_pj|, and
 normwise.  The tensor-core kernel uses fused multiply-adds and its own k order,
 so it is not bit-identical to the reference's separately rounded ascending-p
@@ -190,7 +190,7 @@ def test_empty_dimensions(abi):
 
 
 def test_linearity_at_full_size(abi):
-    """4096^3 (a BASELINE matmul size) without a CPU pass: (A+A').B == A.B + A'.B
+    """4096^3 (a benchmark matmul size) without a CPU pass: (A+A').B == A.B + A'.B
     within the dot-product bound, and A.I == A exactly."""
     n = 4096
     rng = np.random.default_rng(1)

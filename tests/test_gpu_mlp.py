@@ -1,4 +1,4 @@
-"""GPU: the MLP hot path end to end (BASELINE configs 1, 4, 5 at test sizes).
+"""GPU: the MLP hot path end to end (benchmark configs 1, 4, 5 at test sizes).
 
 Linear (fused bias / bias+ReLU GEMM epilogues) -> softmax cross-entropy ->
 backward -> SGD, compared with the reference-generated golden vectors of config
@@ -154,7 +154,7 @@ def _train_both(api, fast, sizes, batch, steps, lr=0.01, seed=0):
 
 
 def test_hundred_steps_of_config4_architecture_at_reduced_batch(api, fast):
-    """784-1024-1024-10, 100 SGD steps (BASELINE config 4's step count) at batch 256:
+    """784-1024-1024-10, 100 SGD steps (benchmark config 4's step count) at batch 256:
     the whole loss curve and the final parameters against the oracle."""
     got, want, layers, ref = _train_both(api, fast, [784, 1024, 1024, 10], 256, 100)
     assert np.max(np.abs(got - want) / np.abs(want)) <= 1e-9
@@ -165,7 +165,7 @@ def test_hundred_steps_of_config4_architecture_at_reduced_batch(api, fast):
 
 
 def test_two_full_batch_steps_of_config4(api, fast):
-    """BASELINE config 4 at its full size (global batch 65536): two SGD steps against
+    """Benchmark config 4 at its full size (global batch 65536): two SGD steps against
     the multi-threaded order-preserving oracle (about half a minute of host time)."""
     got, want, layers, ref = _train_both(api, fast, [784, 1024, 1024, 10], 65536, 2)
     assert np.max(np.abs(got - want) / np.abs(want)) <= 1e-10

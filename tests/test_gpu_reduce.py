@@ -1,7 +1,7 @@
 """GPU parity: reductions, row broadcast gradients, softmax cross-entropy and
 argmax through the device C ABI against the CPU oracle.
 
-Tolerance (BASELINE north_star): rel err <= 1e-10 for reductions.  Errors are
+Tolerance (the stated parity bar): rel err <= 1e-10 for reductions.  Errors are
 measured against the natural scale of the sum (sum of |x|), because the
 reference's own left-to-right sum carries a rounding error of that order: with
 cancellation |sum| can be far smaller than the error bound of either side.
