@@ -121,6 +121,33 @@ def test_relu_edge_values(abi):
     assert np.array_equal(got, expect) and not np.signbit(got[1])
 
 
+def test_tanh_edge_values_and_ulp_bound(abi):
+    """The device tanh is a single-path expm1 form: signed zeros, subnormals,
+    saturation, infinities and NaN behave like std::tanh, and over a wide range of
+    magnitudes the result stays within 4 units in the last place of libm's."""
+    x = np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 1e-320, -1e-320, 5e-324,
+                  19.0, -19.5, 20.0, 25.0, 1e300, -1e300, 0.5493061443340549, -0.17328679513998632])
+    dx, out = abi.array(x), abi.empty(x.size)
+    abi.mg_unary_fwd(K.TANH, dx.ptr, 0.0, out.ptr, x.size)
+    got, ref = out.numpy(), np.tanh(x)
+    assert np.isnan(got[4])
+    assert np.array_equal(np.signbit(got), np.signbit(ref))
+    assert np.array_equal(got[:4], ref[:4]) and np.array_equal(got[5:8], ref[5:8])
+    finite = ~np.isnan(ref)
+    assert np.all(np.abs(got[finite] - ref[finite]) <= 4 * np.spacing(np.abs(ref[finite])))
+
+    rng = np.random.default_rng(77)
+    n = 1 << 18
+    mags = np.concatenate([rng.standard_normal(n), rng.uniform(-22, 22, n),
+                           np.ldexp(rng.uniform(0.5, 1.0, n), -rng.integers(0, 1074, n))
+                           * rng.choice([-1.0, 1.0], n)])
+    dm, om = abi.array(mags), abi.empty(mags.size)
+    abi.mg_unary_fwd(K.TANH, dm.ptr, 0.0, om.ptr, mags.size)
+    got, ref = om.numpy(), np.tanh(mags)
+    assert np.all(np.abs(got - ref) <= 4 * np.spacing(np.abs(ref)))
+    assert np.all(np.abs(got) <= 1.0)
+
+
 def test_unaligned_pointers_take_scalar_path(abi, fast):
     """Buffers that start 8 bytes off a 16-byte boundary (slices of a larger
     allocation) must give the same bits as aligned ones."""
