@@ -327,7 +327,10 @@ def run_product(args):
         if world == 1 and not args.no_cpu_baseline:
             cpu_baseline = reference_sample(budget_s=20.0)
 
+    exchange = "none (one rank)"
     if world > 1:
+        exchange = ("peer-memory all-reduce kernel (rank-ordered sums over NVLink peer loads/stores)"
+                    if abi.mg_comm_peer_path(None) else "ncclAllReduce")
         api.comm_shutdown()
         dist.destroy_process_group()
     if rank != 0:
@@ -341,7 +344,7 @@ def run_product(args):
         "scaling": "strong", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
         "config": {"workload": "MLP 784-1024-1024-10 fp64 train step (benchmark config 4)",
                    "global_batch": batch, "rows_per_gpu": rows, "lr": LR, "parallelism": f"dp{world}",
-                   "input_grad": False, "l2": "per-step working set (activations+gradients > 1 GB "
+                   "gradient_exchange": exchange, "input_grad": False, "l2": "per-step working set (activations+gradients > 1 GB "
                    "at N=1, > 300 MB at N=8) exceeds the 126 MB L2"},
         "step_tflops": FLOP_PER_SAMPLE * batch / (ms_per_step * 1e-3) / 1e12 / world,
         "final_loss": final_loss,

@@ -193,15 +193,35 @@ int mg_event_destroy(int id);
 int mg_event_wait_bounded(int id, double timeout_s);
 
 /* ---- data-parallel communication (no counterpart in the reference) ------ */
-/* NCCL over NVLink.  The all-reduce runs on a separate comm stream, ordered
- * after everything enqueued on the compute stream so far; the compute stream
- * does not wait for it until mg_comm_join(). */
+/* One process per GPU over NVLink.  The all-reduce runs on a separate comm
+ * stream, ordered after everything enqueued on the compute stream so far; the
+ * compute stream does not wait for it until mg_comm_join().
+ *
+ * mg_allreduce_sum_async() on a range of a buffer from mg_comm_alloc_shared()
+ * (even element offset and count, 2/4/8 ranks) runs this library's own kernel
+ * over peer memory: rank r pulls slice r of the range from every rank, adds the
+ * copies in rank order and stores the sums into every rank's buffer, so all
+ * ranks hold bit-identical results.  Its waits on other ranks are bounded (about
+ * ten seconds, or MG_PEER_WAIT_MS); an expired wait raises the kernel fault word (codes 301/302,
+ * reported by mg_check_kernel_status()).  Any other buffer goes through
+ * ncclAllReduce; MG_ALLREDUCE=nccl in the environment forces that everywhere.
+ * All ranks must issue the same sequence of calls. */
 int mg_comm_unique_id(char *out128_host);
 int mg_comm_init(const char *id128_host, int rank, int world);
 int mg_comm_destroy(void);
 int mg_comm_rank(void);
 int mg_comm_world(void);
 int mg_allreduce_sum_async(double *buf, size_t n);
+/* Collective over the communicator (every rank calls it, in the same order, with
+ * the same n): a zero-filled device buffer of n doubles that every rank maps
+ * through CUDA IPC.  If any rank cannot map any peer, every rank keeps a plain
+ * local buffer and its all-reduces use NCCL.  Without a communicator the call
+ * returns a plain local buffer.  Free with mg_comm_free_shared() (not mg_free). */
+int mg_comm_alloc_shared(size_t n, double **out);
+int mg_comm_free_shared(double *ptr);
+/* 1 if all-reduces on the shared buffer containing ptr use the peer-memory
+ * kernel; with ptr == NULL, 1 if any live shared buffer does. */
+int mg_comm_peer_path(const double *ptr);
 int mg_comm_join(void); /* compute stream waits for all all-reduces enqueued so far */
 /* Polls NCCL's async error state and the comm stream up to timeout_s; aborts
  * the communicator and returns MG_ERR_TIMEOUT / MG_ERR_NCCL on failure. */

@@ -87,6 +87,9 @@ SIGNATURES = {
     "mg_comm_rank": (C.c_int, []),
     "mg_comm_world": (C.c_int, []),
     "mg_allreduce_sum_async": (C.c_int, [C.c_void_p, _sz]),
+    "mg_comm_alloc_shared": (C.c_int, [_sz, C.POINTER(C.c_void_p)]),
+    "mg_comm_free_shared": (C.c_int, [C.c_void_p]),
+    "mg_comm_peer_path": (C.c_int, [C.c_void_p]),
     "mg_comm_join": (C.c_int, []),
     "mg_comm_wait_bounded": (C.c_int, [C.c_double]),
     "mg_probe_dmma_tflops": (C.c_int, [C.c_int, C.c_int, _dp]),
@@ -95,7 +98,7 @@ SIGNATURES = {
 }
 
 # Entry points whose int result is a value, not a status.
-_VALUE_INT = {"mg_device", "mg_sm_count", "mg_comm_rank", "mg_comm_world"}
+_VALUE_INT = {"mg_device", "mg_sm_count", "mg_comm_rank", "mg_comm_world", "mg_comm_peer_path"}
 
 
 def declared_in_header(header_text: str) -> list[str]:

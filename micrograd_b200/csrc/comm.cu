@@ -1,6 +1,17 @@
-// Data-parallel gradient exchange: NCCL all-reduce over NVLink on a dedicated
-// stream, event-chained to the compute stream so it overlaps the rest of the
-// backward pass.
+// Data-parallel gradient exchange on a dedicated high-priority stream,
+// event-chained to the compute stream so it overlaps the rest of the backward
+// pass.  Two paths:
+//
+//  * Buffers obtained from mg_comm_alloc_shared() are mapped into every rank's
+//    address space (CUDA IPC over NVLink peer access).  Their all-reduce is one
+//    kernel of this file: rank r pulls slice r of the message from every peer
+//    with plain loads, adds the W copies in rank order (so every rank ends up
+//    with bit-identical sums, whatever the arrival order) and stores the result
+//    into all W buffers.  Two flag rounds (inputs ready / results delivered)
+//    bracket the data movement; every wait is bounded and reports through the
+//    kernel fault word.  No multicast loads are used.
+//  * Any other buffer, or a job whose ranks could not map each other's memory,
+//    goes through ncclAllReduce.
 //
 // NCCL is bound at run time (dlopen) rather than at link time: the library
 // loads on machines without NCCL, and inside a process that has already loaded
@@ -14,6 +25,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <thread>
+#include <vector>
 
 namespace mg {
 namespace {
@@ -26,9 +38,22 @@ struct NcclApi {
   decltype(&ncclCommDestroy) CommDestroy = nullptr;
   decltype(&ncclCommAbort) CommAbort = nullptr;
   decltype(&ncclAllReduce) AllReduce = nullptr;
+  decltype(&ncclAllGather) AllGather = nullptr;
   decltype(&ncclGetErrorString) GetErrorString = nullptr;
   decltype(&ncclCommGetAsyncError) CommGetAsyncError = nullptr;
 };
+
+// Longest a peer kernel waits for another rank, in SM clock cycles: about ten
+// seconds (ranks of one job can be that far apart while they start up), or
+// MG_PEER_WAIT_MS from the environment.
+long long peer_wait_cycles() {
+  static const long long v = [] {
+    const char *e = std::getenv("MG_PEER_WAIT_MS");
+    const long long ms = e && *e ? std::atoll(e) : 10000;
+    return (ms < 1 ? 1 : ms) * 1965000ll;
+  }();
+  return v;
+}
 
 NcclApi g_nccl;
 ncclComm_t g_comm = nullptr;
@@ -51,6 +76,7 @@ int load_nccl() {
   MG_NCCL_SYM(CommDestroy, ncclCommDestroy)
   MG_NCCL_SYM(CommAbort, ncclCommAbort)
   MG_NCCL_SYM(AllReduce, ncclAllReduce)
+  MG_NCCL_SYM(AllGather, ncclAllGather)
   MG_NCCL_SYM(GetErrorString, ncclGetErrorString)
   MG_NCCL_SYM(CommGetAsyncError, ncclCommGetAsyncError)
 #undef MG_NCCL_SYM
@@ -63,6 +89,200 @@ int load_nccl() {
 int nccl_fail(ncclResult_t r, const char *what) {
   return fail(MG_ERR_NCCL, "NCCL error %d (%s) in %s", (int)r,
               g_nccl.GetErrorString ? g_nccl.GetErrorString(r) : "?", what);
+}
+
+
+// ---------------------------------------------------------------------------
+// Peer-memory all-reduce
+// ---------------------------------------------------------------------------
+constexpr int kMaxPeers = 8;
+constexpr int kPeerThreads = 512;
+constexpr size_t kFlagBytes = 256;  // ready[8] + done[8] (u32) + CTA ticket, padded
+
+struct SharedBuffer {
+  double *base = nullptr;   // this rank's allocation: n doubles followed by the flag block
+  size_t elems = 0;
+  bool peers_mapped = false;
+  double *peer[kMaxPeers] = {};  // peer[q]: rank q's allocation as seen from this process
+  unsigned seq = 0;              // all-reduce calls issued on this buffer so far
+};
+
+std::vector<SharedBuffer> g_shared;
+
+struct PeerArgs {
+  double *data[kMaxPeers];     // every rank's buffer, indexed by rank
+  unsigned *flags[kMaxPeers];  // every rank's flag block
+  int rank;
+  unsigned seq;
+  size_t offset, n;            // message = elements [offset, offset + n) of each buffer; both even
+  long long wait_cycles;
+  int *status;
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ double2 ld_peer(const double2 *p) {
+  double2 v;
+  asm volatile("ld.relaxed.sys.global.v2.f64 {%0, %1}, [%2];" : "=d"(v.x), "=d"(v.y) : "l"(p) : "memory");
+  return v;
+}
+
+// Waits until *flag has reached `seq` (flags only ever grow).  Gives up after
+// `limit` clock cycles; the caller then raises the fault word and carries on
+// without touching peer data, so a missing rank cannot hang this GPU.
+__device__ __forceinline__ bool wait_flag(const unsigned *flag, unsigned seq, long long limit) {
+  const long long start = clock64();
+  for (;;) {
+    if ((int)(ld_acquire_sys(flag) - seq) >= 0) return true;
+    if (clock64() - start > limit) return false;
+    __nanosleep(64);
+  }
+}
+
+// Flag block layout (u32): [0, 8) ready[src rank], [8, 16) done[src rank], [16] CTA ticket.
+template <int W>
+__global__ void __launch_bounds__(kPeerThreads) peer_allreduce_kernel(PeerArgs a) {
+  __shared__ int ok_s, last_s;
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    ok_s = 1;
+    last_s = 0;
+  }
+  __syncthreads();
+  unsigned *mine = a.flags[a.rank];
+
+  // Round 1: tell every rank that this rank's inputs are final (they were written
+  // by kernels that completed before this one started), then wait for theirs.
+  if (blockIdx.x == 0 && tid < W) {
+    __threadfence_system();
+    st_release_sys(a.flags[tid] + a.rank, a.seq);
+  }
+  if (tid < W && !wait_flag(mine + tid, a.seq, a.wait_cycles)) {
+    ok_s = 0;
+    atomicExch(a.status, 301);
+  }
+  __syncthreads();
+
+  if (ok_s) {
+    // Slice of the message this rank reduces: W nearly equal parts of whole 16-byte words.
+    const size_t words = a.n >> 1;
+    const size_t per = (words + W - 1) / W;
+    const size_t lo = min(words, per * (size_t)a.rank), hi = min(words, lo + per);
+    const size_t first = (a.offset >> 1) + lo, count = hi - lo;
+    const size_t stride = (size_t)gridDim.x * kPeerThreads;
+    size_t i = (size_t)blockIdx.x * kPeerThreads + tid;
+    // Two words per thread and iteration: 2 W loads in flight before the first add.
+    for (; i + stride < count; i += 2 * stride) {
+      double2 v0[W], v1[W];
+#pragma unroll
+      for (int q = 0; q < W; q++) {
+        const double2 *src = reinterpret_cast<const double2 *>(a.data[q]) + first;
+        v0[q] = ld_peer(src + i);
+        v1[q] = ld_peer(src + i + stride);
+      }
+      double2 s0 = v0[0], s1 = v1[0];
+#pragma unroll
+      for (int q = 1; q < W; q++) {
+        s0.x += v0[q].x; s0.y += v0[q].y;
+        s1.x += v1[q].x; s1.y += v1[q].y;
+      }
+#pragma unroll
+      for (int q = 0; q < W; q++) {
+        double2 *dst = reinterpret_cast<double2 *>(a.data[q]) + first;
+        dst[i] = s0;
+        dst[i + stride] = s1;
+      }
+    }
+    for (; i < count; i += stride) {
+      double2 v[W];
+#pragma unroll
+      for (int q = 0; q < W; q++)
+        v[q] = ld_peer(reinterpret_cast<const double2 *>(a.data[q]) + first + i);
+      double2 s = v[0];
+#pragma unroll
+      for (int q = 1; q < W; q++) { s.x += v[q].x; s.y += v[q].y; }
+#pragma unroll
+      for (int q = 0; q < W; q++) (reinterpret_cast<double2 *>(a.data[q]) + first)[i] = s;
+    }
+  }
+
+  // Round 2: once every CTA of this rank has pushed its results, tell every rank,
+  // and have the last CTA stay until all ranks have said the same — when this
+  // kernel completes, the whole reduced message is in this rank's buffer.
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned prev = atomicAdd(mine + 16, 1u);
+    if (prev == gridDim.x - 1) {
+      mine[16] = 0;  // next call on this buffer starts from zero (calls are stream-ordered)
+      last_s = 1;
+    }
+    __threadfence_system();
+  }
+  __syncthreads();
+  if (last_s && tid < W) {
+    st_release_sys(a.flags[tid] + 8 + a.rank, a.seq);
+    if (!wait_flag(mine + 8 + tid, a.seq, a.wait_cycles)) atomicExch(a.status, 302);
+  }
+}
+
+int peer_ctas() {
+  static const int v = [] {
+    const char *e = std::getenv("MG_PEER_CTAS");
+    int n = e && *e ? std::atoi(e) : 16;
+    return n < 1 ? 1 : (n > 148 ? 148 : n);
+  }();
+  return v;
+}
+
+bool peer_path_disabled() {
+  static const bool v = [] {
+    const char *e = std::getenv("MG_ALLREDUCE");
+    return e && std::strcmp(e, "nccl") == 0;
+  }();
+  return v;
+}
+
+SharedBuffer *find_shared(const double *buf, size_t n) {
+  for (auto &b : g_shared)
+    if (buf >= b.base && buf + n <= b.base + b.elems) return &b;
+  return nullptr;
+}
+
+template <int W>
+int launch_peer_allreduce(SharedBuffer &b, size_t offset, size_t n) {
+  Context &c = ctx();
+  PeerArgs a;
+  for (int q = 0; q < kMaxPeers; q++) {
+    a.data[q] = q < W ? b.peer[q] : nullptr;
+    a.flags[q] = q < W ? reinterpret_cast<unsigned *>(b.peer[q] + b.elems) : nullptr;
+  }
+  a.rank = g_rank;
+  a.seq = ++b.seq;
+  a.offset = offset;
+  a.n = n;
+  a.wait_cycles = peer_wait_cycles();
+  a.status = c.kernel_status;
+  const size_t words_per_rank = (n / 2 + W - 1) / W;
+  size_t ctas = (words_per_rank + 2 * kPeerThreads - 1) / (2 * kPeerThreads);
+  if (ctas < 1) ctas = 1;
+  if (ctas > (size_t)peer_ctas()) ctas = (size_t)peer_ctas();
+  peer_allreduce_kernel<W><<<(unsigned)ctas, kPeerThreads, 0, c.comm_stream>>>(a);
+  MG_LAUNCH_CHECK("peer_allreduce");
+  return MG_OK;
+}
+
+void unmap_peers(SharedBuffer &b) {
+  if (!b.peers_mapped) return;
+  for (int q = 0; q < g_world && q < kMaxPeers; q++)
+    if (q != g_rank && b.peer[q]) cudaIpcCloseMemHandle(b.peer[q]);
+  b.peers_mapped = false;
 }
 
 }  // namespace
@@ -122,6 +342,9 @@ int mg_comm_init(const char *id128_host, int rank, int world) {
 int mg_comm_destroy(void) {
   if (!g_comm) return MG_OK;
   if (ctx().ready) cudaStreamSynchronize(ctx().comm_stream);
+  // Peer mappings end with the communicator; the local allocations stay until
+  // mg_comm_free_shared() and fall back to plain local buffers.
+  for (auto &b : g_shared) unmap_peers(b);
   ncclResult_t r = g_nccl.CommDestroy(g_comm);
   g_comm = nullptr;
   g_rank = 0;
@@ -145,9 +368,133 @@ int mg_allreduce_sum_async(double *buf, size_t n) {
   // comm stream picks up after everything enqueued on the compute stream so far
   MG_CUDA_TRY(cudaEventRecord(c.fork_event, c.stream));
   MG_CUDA_TRY(cudaStreamWaitEvent(c.comm_stream, c.fork_event, 0));
+  // The choice below depends only on values that are equal on every rank.
+  SharedBuffer *shared = find_shared(buf, n);
+  if (shared && shared->peers_mapped && !peer_path_disabled()) {
+    const size_t offset = (size_t)(buf - shared->base);
+    if (((offset | n) & 1) == 0) {
+      switch (g_world) {
+        case 2: return launch_peer_allreduce<2>(*shared, offset, n);
+        case 4: return launch_peer_allreduce<4>(*shared, offset, n);
+        case 8: return launch_peer_allreduce<8>(*shared, offset, n);
+        default: break;
+      }
+    }
+  }
   ncclResult_t r = g_nccl.AllReduce(buf, buf, n, ncclDouble, ncclSum, g_comm, c.comm_stream);
   if (r != ncclSuccess) return nccl_fail(r, "ncclAllReduce");
   return MG_OK;
+}
+
+int mg_comm_alloc_shared(size_t n, double **out) {
+  MG_ENSURE_INIT();
+  if (!out) return fail(MG_ERR_INVALID, "mg_comm_alloc_shared: null out pointer");
+  *out = nullptr;
+  Context &c = ctx();
+  SharedBuffer b;
+  b.elems = (n + 1) & ~(size_t)1;  // flag block stays 16-byte aligned
+  void *p = nullptr;
+  cudaError_t e = cudaMalloc(&p, b.elems * sizeof(double) + kFlagBytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(e == cudaErrorMemoryAllocation ? MG_ERR_OOM : MG_ERR_CUDA,
+                "shared allocation of %zu doubles failed: %s", n, cudaGetErrorString(e));
+  }
+  b.base = static_cast<double *>(p);
+  MG_CUDA_TRY(cudaMemsetAsync(p, 0, b.elems * sizeof(double) + kFlagBytes, c.comm_stream));
+  MG_CUDA_TRY(cudaStreamSynchronize(c.comm_stream));
+
+  // Map every peer's allocation.  The handles travel through an NCCL all-gather
+  // and a final all-reduce(min) makes the outcome unanimous: either every rank
+  // sees every buffer, or all of them use NCCL for this buffer.
+  const bool want_peers = g_comm && (g_world == 2 || g_world == 4 || g_world == 8);
+  if (want_peers) {
+    struct Record {
+      cudaIpcMemHandle_t handle;
+      int ok;
+      int pad[15];
+    };
+    static_assert(sizeof(Record) == 128, "handle record size");
+    Record mine_rec;
+    std::memset(&mine_rec, 0, sizeof(mine_rec));
+    mine_rec.ok = cudaIpcGetMemHandle(&mine_rec.handle, p) == cudaSuccess ? 1 : 0;
+    cudaGetLastError();
+    Record *dev = nullptr;
+    std::vector<Record> all((size_t)g_world);
+    MG_CUDA_TRY(cudaMalloc(&dev, sizeof(Record) * (size_t)(g_world + 1)));
+    MG_CUDA_TRY(cudaMemcpyAsync(dev + g_world, &mine_rec, sizeof(Record), cudaMemcpyHostToDevice,
+                                c.comm_stream));
+    ncclResult_t r = g_nccl.AllGather(dev + g_world, dev, sizeof(Record), ncclChar, g_comm,
+                                      c.comm_stream);
+    if (r != ncclSuccess) {
+      cudaFree(dev);
+      cudaFree(p);
+      return nccl_fail(r, "ncclAllGather(handles)");
+    }
+    MG_CUDA_TRY(cudaMemcpyAsync(all.data(), dev, sizeof(Record) * (size_t)g_world,
+                                cudaMemcpyDeviceToHost, c.comm_stream));
+    MG_CUDA_TRY(cudaStreamSynchronize(c.comm_stream));
+    double ok = 1.0;
+    for (int q = 0; q < g_world; q++) {
+      if (q == g_rank) {
+        b.peer[q] = b.base;
+        continue;
+      }
+      void *mapped = nullptr;
+      if (!all[(size_t)q].ok ||
+          cudaIpcOpenMemHandle(&mapped, all[(size_t)q].handle, cudaIpcMemLazyEnablePeerAccess) !=
+              cudaSuccess) {
+        cudaGetLastError();
+        ok = 0.0;
+        continue;
+      }
+      b.peer[q] = static_cast<double *>(mapped);
+    }
+    if (!mine_rec.ok) ok = 0.0;
+    double *vote = reinterpret_cast<double *>(dev);
+    MG_CUDA_TRY(cudaMemcpyAsync(vote, &ok, sizeof(double), cudaMemcpyHostToDevice, c.comm_stream));
+    r = g_nccl.AllReduce(vote, vote, 1, ncclDouble, ncclMin, g_comm, c.comm_stream);
+    if (r != ncclSuccess) {
+      cudaFree(dev);
+      cudaFree(p);
+      return nccl_fail(r, "ncclAllReduce(vote)");
+    }
+    MG_CUDA_TRY(cudaMemcpyAsync(&ok, vote, sizeof(double), cudaMemcpyDeviceToHost, c.comm_stream));
+    MG_CUDA_TRY(cudaStreamSynchronize(c.comm_stream));
+    cudaFree(dev);
+    b.peers_mapped = true;  // so that unmap_peers() closes what was opened
+    if (ok < 1.0) unmap_peers(b);
+  }
+  g_shared.push_back(b);
+  *out = b.base;
+  return MG_OK;
+}
+
+int mg_comm_free_shared(double *ptr) {
+  if (!ptr) return MG_OK;
+  for (size_t i = 0; i < g_shared.size(); i++) {
+    if (g_shared[i].base != ptr) continue;
+    if (ctx().ready) {
+      cudaStreamSynchronize(ctx().comm_stream);
+      cudaStreamSynchronize(ctx().stream);
+    }
+    unmap_peers(g_shared[i]);
+    cudaFree(g_shared[i].base);
+    g_shared.erase(g_shared.begin() + (long)i);
+    return MG_OK;
+  }
+  return fail(MG_ERR_INVALID, "mg_comm_free_shared: pointer was not returned by mg_comm_alloc_shared");
+}
+
+int mg_comm_peer_path(const double *ptr) {
+  if (peer_path_disabled()) return 0;
+  if (ptr) {
+    SharedBuffer *b = find_shared(ptr, 0);
+    return (b && b->peers_mapped) ? 1 : 0;
+  }
+  for (auto &b : g_shared)
+    if (b.peers_mapped) return 1;
+  return 0;
 }
 
 int mg_comm_join(void) {

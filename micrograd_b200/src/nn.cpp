@@ -199,9 +199,14 @@ namespace {
 struct FlatBuffers {
   double *data = nullptr;
   double *grad = nullptr;
+  bool grad_shared = false;  // grad came from mg_comm_alloc_shared
   ~FlatBuffers() {
     mg_free(data);
-    mg_free(grad);
+    if (grad_shared) {
+      mg_comm_free_shared(grad);
+    } else {
+      mg_free(grad);
+    }
   }
 };
 }  // namespace
@@ -221,9 +226,16 @@ void SGD::enable_allreduce() {
   flat_elems_ = total;
   auto flat = std::make_shared<FlatBuffers>();
   check(mg_alloc(total, &flat->data), "device allocation");
-  check(mg_alloc(total, &flat->grad), "device allocation");
   check(mg_fill(flat->data, 0.0, total), "fill");
-  check(mg_fill(flat->grad, 0.0, total), "fill");
+  if (micrograd::comm_world() > 1) {
+    // Gradients of a multi-rank job live in a buffer every rank maps, so the
+    // exchange can run over peer memory (all ranks reach this call together).
+    check(mg_comm_alloc_shared(total, &flat->grad), "shared gradient buffer");
+    flat->grad_shared = true;
+  } else {
+    check(mg_alloc(total, &flat->grad), "device allocation");
+    check(mg_fill(flat->grad, 0.0, total), "fill");
+  }
   flat_data_ = flat->data;
   flat_grad_ = flat->grad;
   for (size_t i = 0; i < parameters_.size(); i++) {

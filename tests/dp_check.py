@@ -5,7 +5,11 @@
 
 Every rank trains the same MLP for a few SGD steps on its row shard of a global
 batch through the public Tensor API, with parameter gradients summed across
-ranks by the library's NCCL all-reduce (started from backward()).  Rank 0
+ranks by the library's all-reduce (started from backward(); the peer-memory
+kernel where ranks can map each other's buffers, NCCL otherwise).  Before that
+the all-reduce itself is checked on a shared buffer: sub-ranges at even offsets
+must equal the rank-ordered sum bit for bit on every rank, and agree with the
+NCCL path on a plain buffer.  Rank 0
 compares losses and final parameters with the CPU oracle's full-batch training
 (normwise <= 1e-9) and prints DP_PARITY_OK.  Also checks that sharded inference
 yields the oracle's argmax ids on every rank's rows.
@@ -24,6 +28,53 @@ import micrograd_b200  # noqa: E402
 from micrograd_b200.dist import env_rank_world, init_comm, shard_rows  # noqa: E402
 
 
+def check_allreduce(abi, rank, world):
+    """Peer-memory all-reduce against the rank-ordered sum computed on the host."""
+    import ctypes as C
+    n = 200_000
+    per_rank = [np.random.default_rng(1000 + q).standard_normal(n) for q in range(world)]
+    shared = C.c_void_p()
+    abi.mg_comm_alloc_shared(n, C.byref(shared))
+    peer = abi.mg_comm_peer_path(shared.value)
+    plain = abi.array(per_rank[rank])
+    abi.mg_upload(shared.value, per_rank[rank].ctypes.data, n)
+    ranges = [(0, 4096), (4096, 150_000), (154_096, 2), (160_000, 39_998)]   # (offset, count), even
+    for _ in range(3):                       # repeated calls reuse the flags
+        for off, cnt in ranges:
+            abi.mg_allreduce_sum_async(shared.value + 8 * off, cnt)
+    for off, cnt in ranges:
+        abi.mg_allreduce_sum_async(plain.ptr + 8 * off, cnt)   # not a shared buffer: NCCL
+    abi.mg_comm_join()
+    abi.mg_sync()
+    abi.mg_check_kernel_status()
+    got = np.empty(n)
+    abi.mg_download(got.ctypes.data, shared.value, n)
+    nccl = plain.numpy()
+    ok = True
+    for off, cnt in ranges:
+        once = per_rank[0][off:off + cnt].copy()
+        for q in range(1, world):
+            once = once + per_rank[q][off:off + cnt]          # rank order, like the kernel
+        twice = once.copy()
+        for _ in range(world - 1):
+            twice = twice + once                               # second call sums W equal copies
+        thrice = twice.copy()
+        for _ in range(world - 1):
+            thrice = thrice + twice
+        if peer:
+            ok = ok and np.array_equal(got[off:off + cnt], thrice)
+        else:
+            ok = ok and np.allclose(got[off:off + cnt], thrice, rtol=1e-13, atol=0)
+        ok = ok and np.allclose(nccl[off:off + cnt], once, rtol=1e-13, atol=1e-300)
+    untouched = np.ones(n, dtype=bool)
+    for off, cnt in ranges:
+        untouched[off:off + cnt] = False
+    ok = ok and np.array_equal(got[untouched], per_rank[rank][untouched])
+    abi.mg_comm_free_shared(shared.value)
+    print(f"rank {rank}: allreduce check {'ok' if ok else 'FAILED'} peer_path={peer}", flush=True)
+    return ok, peer
+
+
 def main():
     rank, world, local_rank = env_rank_world()
     torch.cuda.set_device(local_rank)
@@ -33,6 +84,7 @@ def main():
     api = micrograd_b200.load_api()
     init_comm(api)
     assert api.comm_world() == world and api.comm_rank() == rank
+    allreduce_ok, peer = check_allreduce(abi, rank, world)
 
     rng = np.random.default_rng(77)                      # identical on all ranks
     sizes, batch, steps, lr = [784, 256, 128, 10], 1024, 4, 0.05
@@ -70,7 +122,7 @@ def main():
     import oracle
     fast = oracle.fast
     ref = [(W.copy(), bias.copy()) for W, bias in params]
-    ok = True
+    ok = allreduce_ok
     for s in range(steps):
         ref_loss, _, _ = fast.mlp_train_step(ref, X, y, lr)
         if abs(losses[s] - ref_loss) > 1e-10 * abs(ref_loss):
@@ -93,7 +145,8 @@ def main():
     api.comm_shutdown()
     dist.destroy_process_group()
     if rank == 0:
-        print("DP_PARITY_OK" if int(flag.item()) == 1 else "DP_PARITY_FAILED", f"world={world} losses={losses}")
+        print("DP_PARITY_OK" if int(flag.item()) == 1 else "DP_PARITY_FAILED",
+              f"world={world} peer_path={peer} losses={losses}")
     sys.exit(0 if int(flag.item()) == 1 else 1)
 
 
