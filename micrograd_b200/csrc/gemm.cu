@@ -62,6 +62,11 @@ using MainCfg = TileCfg<4, 4, 4, 6>;
 // All eight warps split the rows, so the MMAs spread over the four SM
 // sub-partitions instead of landing on the one that owns a single warp column.
 using SkinnyCfg = TileCfg<1, 1, 4, 8>;
+// 128 x 16, eight 18 KB stages: outputs at most 16 columns wide.  Such a problem
+// streams its tall operand once and is bound by HBM only if the MMAs on padding
+// columns stay below the copy time: at 32 columns the 10-logit layer spent 0.52 us
+// of tensor-pipe time per k-tile against 0.37 us of copy time, at 16 it is 0.26.
+using Skinny16Cfg = TileCfg<1, 1, 2, 8>;
 // 128 x 64, eight 24 KB stages: used when 128 x 128 tiles would leave the last
 // wave of CTAs mostly empty (e.g. 512 tiles on 148 SMs).
 using HalfCfg = TileCfg<2, 2, 4, 8>;
@@ -637,13 +642,15 @@ static int launch_tiles(const DmmaLaunch &L) {
   return launch_dmma_kernel<AK, BK_, SHAPE, false, Cfg>(L);
 }
 
-enum TileChoice { kTileMain = 0, kTileSkinny = 1, kTileHalf = 2, kTileRows112 = 3 };
+enum TileChoice { kTileMain = 0, kTileSkinny = 1, kTileHalf = 2, kTileRows112 = 3, kTileSkinny16 = 4 };
 
 template <bool AK, bool BK_>
 static int launch_layout(int shape, int tile, const DmmaLaunch &L) {
   // The narrow and half-width configurations exist for the default mma shape only.
   if (tile == kTileSkinny)
     return launch_dmma_kernel<AK, BK_, 2, true, SkinnyCfg>(L);
+  if (tile == kTileSkinny16)
+    return launch_dmma_kernel<AK, BK_, 2, true, Skinny16Cfg>(L);
   if (tile == kTileHalf) return launch_tiles<AK, BK_, 2, HalfCfg>(L);
   if (tile == kTileRows112) return launch_tiles<AK, BK_, 2, Rows112Cfg>(L);
   switch (shape) {
@@ -687,6 +694,10 @@ struct GemmPlan {
 static GemmPlan choose_plan(int M, int N, int K, int sms, int shape) {
   const int KT = (K + BK - 1) / BK;
   auto tiles_of = [&](int bm, int bn) { return ((M + bm - 1) / bm) * ((N + bn - 1) / bn); };
+  if (N <= Skinny16Cfg::BN) {
+    return {kTileSkinny16, Skinny16Cfg::BM, Skinny16Cfg::BN,
+            choose_splits(tiles_of(Skinny16Cfg::BM, Skinny16Cfg::BN), KT, sms)};
+  }
   if (N <= SkinnyCfg::BN) {
     return {kTileSkinny, SkinnyCfg::BM, SkinnyCfg::BN,
             choose_splits(tiles_of(SkinnyCfg::BM, SkinnyCfg::BN), KT, sms)};
