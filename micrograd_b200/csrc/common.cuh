@@ -55,6 +55,9 @@ int cuda_fail(cudaError_t e, const char *what);
 // Grows a scratch buffer (stream-ordered free + alloc) to at least `elems`.
 int ensure_scratch(double **buf, size_t *have, size_t elems);
 
+// Frees the segment tables the GEMM dispatcher caches on the device.
+void gemm_release_tables();
+
 inline void count_launch() { ctx().launches++; }
 
 #define MG_CUDA_TRY(expr)                                                                          \

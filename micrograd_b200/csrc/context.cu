@@ -135,6 +135,7 @@ int mg_shutdown(void) {
   if (c.colsum_scratch) cudaFreeAsync(c.colsum_scratch, c.stream);
   if (c.splitk_scratch) cudaFreeAsync(c.splitk_scratch, c.stream);
   cudaStreamSynchronize(c.stream);
+  gemm_release_tables();
   cudaFree(c.reduce_partials);
   cudaFree(c.reduce_ticket);
   cudaFree(c.kernel_status);

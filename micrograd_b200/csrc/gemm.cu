@@ -19,9 +19,13 @@
 //     epilogue adds the bias, applies ReLU or the ReLU mask, and stores or
 //     accumulates 16 bytes per thread per row, all loads before the stores.
 //   - When the output has too few tiles to fill 148 SMs (weight gradients: the
-//     contraction runs over the batch), the contraction is split across the grid
-//     and a second kernel folds the partial tiles in index order, so the result
-//     is still reproducible.
+//     contraction runs over the batch), the (tile, k-tile) iteration space is cut
+//     into one equal span per SM; a span that crosses a tile boundary becomes two
+//     segments.  Every segment is one CTA; segments are issued longest first, so
+//     the hardware scheduler pairs each SM's long piece with the complementary
+//     short one and all SMs finish together.  Tiles covered by several segments
+//     are written as packed partial tiles and folded in k order by a second
+//     kernel, so the result is still reproducible.
 //   - Short work items run as a persistent grid (one CTA per SM looping over
 //     items, the producer prefetching across items); long ones as one item per
 //     CTA under the hardware scheduler.
@@ -31,8 +35,10 @@
 #include "common.cuh"
 #include "tma.cuh"
 
+#include <algorithm>
 #include <cstdlib>
 #include <type_traits>
+#include <vector>
 
 namespace mg {
 
@@ -79,7 +85,7 @@ using Rows112Cfg = TileCfg<8, 7, 2, 6>;
 struct GemmEpilogue {
   double *D;            // output [M][N]
   const double *aux;    // bias[N] or mask source [M][N]
-  double *partial;      // split-K scratch [splits][M*N], or null
+  double *partial;      // packed partial tiles [slot][BM][BN] of split tiles, or null
   int mode;             // MG_EPI_*
   int accumulate;       // D += instead of D =
 };
@@ -232,35 +238,37 @@ __device__ __forceinline__ bool consumer_loop(double (&acc)[Cfg::MT][Cfg::NT][4]
 // then is the per-warp skipping compiled in.
 // One unit of work of a launch: an output tile and a range of k-tiles.
 struct WorkItem {
-  int m0, n0, kt_begin, nkt, split;
+  int m0, n0, kt_begin, nkt;
+  int slot;  // >= 0: write a packed partial tile into this slot; < 0: final epilogue
 };
 
-// Work order.  Tiles are numbered row-major; the first `heavy_tiles` of them are
-// (at least half) full, the remaining `light_tiles` are the thin bottom border of
-// a ragged problem.  Items are issued split by split over the heavy tiles (CTAs
-// working at the same time then share one k-range of both operands in L2), and
-// all light tiles come last, so that short items fill the tail instead of
-// pushing full ones into an extra round.
+// One segment of a split contraction, as laid out by the host (32 bytes).
+struct SegItem {
+  int m0, n0, kt_begin, nkt, slot, pad0, pad1, pad2;
+};
+
+// Work order without a segment table: whole tiles, numbered row-major, so the
+// thin bottom border of a ragged problem comes last and its short items fill the
+// tail instead of pushing full ones into an extra round.
 template <class Cfg>
-__device__ __forceinline__ WorkItem decode_work(int id, int tiles_n, int heavy_tiles, int light_tiles,
-                                                int splits, int kt_per_split, int KT) {
-  int tile, split;
-  const int heavy_items = heavy_tiles * splits;
-  if (id < heavy_items) {
-    split = id / heavy_tiles;
-    tile = id - split * heavy_tiles;
-  } else {
-    const int j = id - heavy_items;
-    split = j / light_tiles;
-    tile = heavy_tiles + (j - split * light_tiles);
-  }
-  const int tile_m = tile / tiles_n, tile_n = tile - tile_m * tiles_n;
+__device__ __forceinline__ WorkItem decode_work(int id, int tiles_n, int KT,
+                                                const SegItem *__restrict__ table) {
   WorkItem w;
+  if (table) {
+    const int4 a = __ldg(reinterpret_cast<const int4 *>(table + id));
+    w.m0 = a.x;
+    w.n0 = a.y;
+    w.kt_begin = a.z;
+    w.nkt = a.w;
+    w.slot = __ldg(&table[id].slot);
+    return w;
+  }
+  const int tile_m = id / tiles_n, tile_n = id - tile_m * tiles_n;
   w.m0 = tile_m * Cfg::BM;
   w.n0 = tile_n * Cfg::BN;
-  w.split = split;
-  w.kt_begin = split * kt_per_split;
-  w.nkt = min(KT, w.kt_begin + kt_per_split) - w.kt_begin;
+  w.kt_begin = 0;
+  w.nkt = KT;
+  w.slot = -1;
   return w;
 }
 
@@ -274,8 +282,8 @@ __device__ __forceinline__ WorkItem decode_work(int id, int tiles_n, int heavy_t
 template <bool A_KCONTIG, bool B_KCONTIG, int SHAPE, bool EDGE, class Cfg, bool PERSISTENT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-                 GemmEpilogue ep, int M, int N, int K, int tiles_n, int heavy_tiles, int light_tiles,
-                 int splits, int kt_per_split, int grouped_ab, int total_items, int *status) {
+                 GemmEpilogue ep, int M, int N, int K, int tiles_n,
+                 const SegItem *__restrict__ table, int grouped_ab, int total_items, int *status) {
   constexpr int BM = Cfg::BM, BN = Cfg::BN, MT = Cfg::MT, NT = Cfg::NT;
   constexpr int kStages = Cfg::STAGES, kStageBytes = Cfg::STAGE_BYTES, kTileBytes = Cfg::A_BYTES;
   extern __shared__ uint8_t smem_raw[];
@@ -310,8 +318,7 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
       bool alive = true;
       int id = blockIdx.x;
       do {
-        const WorkItem w =
-            decode_work<Cfg>(id, tiles_n, heavy_tiles, light_tiles, splits, kt_per_split, KT);
+        const WorkItem w = decode_work<Cfg>(id, tiles_n, KT, table);
         for (int it = 0; it < w.nkt; ++it, ++ring) {
           const unsigned s = ring % kStages;
           if (ring >= (unsigned)kStages) {
@@ -358,9 +365,8 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
 
     int id = blockIdx.x;
     do {
-      const WorkItem w =
-          decode_work<Cfg>(id, tiles_n, heavy_tiles, light_tiles, splits, kt_per_split, KT);
-      const int m0 = w.m0, n0 = w.n0, split = w.split;
+      const WorkItem w = decode_work<Cfg>(id, tiles_n, KT, table);
+      const int m0 = w.m0, n0 = w.n0;
 
       double acc[MT][NT][4];
 #pragma unroll
@@ -387,8 +393,14 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
       // the stores.  Interleaving load/store pairs would serialise them (a store
       // may alias the next load as far as the compiler can tell) and turn the
       // epilogue into a chain of exposed memory latencies.
-      double *dst = ep.partial ? ep.partial + (size_t)split * (size_t)M * (size_t)N : ep.D;
-      const bool direct = (ep.partial == nullptr);
+      // A segment of a split tile stores its whole BM x BN accumulator, packed,
+      // into its slot of the scratch buffer (rows and columns beyond the matrix
+      // hold zeros or are never read); everything else goes to D with bounds.
+      const bool direct = w.slot < 0;
+      double *dst = direct ? ep.D : ep.partial + (size_t)w.slot * (size_t)(BM * BN);
+      const size_t ld = direct ? (size_t)N : (size_t)BN;
+      const int row_base = direct ? 0 : m0, col_base = direct ? 0 : n0;
+      const int row_end = direct ? M : m0 + BM, col_end = direct ? N : n0 + BN;
       const bool use_mask = direct && ep.mode == MG_EPI_RELU_MASK;
       const bool use_bias = direct && (ep.mode == MG_EPI_BIAS || ep.mode == MG_EPI_BIAS_RELU);
       const bool use_old = direct && ep.accumulate;
@@ -410,7 +422,7 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
             for (int nt = 0; nt < NT; nt++) {
               const int col = n0 + wn + nt * 8 + 2 * t;
               const bool in = row < M && col < N;
-              const size_t at = (size_t)row * (size_t)N + (size_t)col;
+              const size_t at = (size_t)row * (size_t)N + (size_t)col;  // only used when direct
               mask[h][nt] = (use_mask && in) ? __ldcs(reinterpret_cast<const double2 *>(ep.aux + at))
                                              : make_double2(0.0, 0.0);
               old[h][nt] = (use_old && in) ? __ldcs(reinterpret_cast<const double2 *>(ep.D + at))
@@ -421,12 +433,12 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
 #pragma unroll
         for (int h = 0; h < 2; h++) {
           const int row = m0 + wm + mt * 16 + g + 8 * h;
-          if (row >= M) continue;
+          if (row >= row_end) continue;
 #pragma unroll
           for (int nt = 0; nt < NT; nt++) {
             const int col = n0 + wn + nt * 8 + 2 * t;
-            if (col >= N) continue;
-            const size_t at = (size_t)row * (size_t)N + (size_t)col;
+            if (col >= col_end) continue;
+            const size_t at = (size_t)(row - row_base) * ld + (size_t)(col - col_base);
             double2 v = make_double2(acc[mt][nt][2 * h], acc[mt][nt][2 * h + 1]);
             if (use_bias) {
               v.x += bias[nt].x;
@@ -464,21 +476,34 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
   }
 }
 
-// Folds split-K partial tiles in index order and applies the epilogue.
+// Folds the packed partial tiles of every split output tile in k order and
+// applies the epilogue.  tile_segs[t] = (first slot, number of segments) of tile
+// t; tiles written directly by a single segment have count 0.  grid = (tiles, 4):
+// blockIdx.y takes a quarter of the tile's rows.
 __global__ void __launch_bounds__(256)
-splitk_finish_kernel(const double *__restrict__ partial, int splits, size_t MN, int N,
-                     GemmEpilogue ep) {
-  const size_t nvec = MN >> 1;
-  const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+splitk_finish_kernel(const double *__restrict__ partial, const int2 *__restrict__ tile_segs,
+                     int tiles_n, int BM, int BN, int M, int N, GemmEpilogue ep) {
+  const int2 seg = __ldg(tile_segs + blockIdx.x);
+  if (seg.y == 0) return;
+  const int tile_m = blockIdx.x / tiles_n, tile_n = blockIdx.x - tile_m * tiles_n;
+  const int words_per_row = BN >> 1;
+  const int rows_here = (BM + (int)gridDim.y - 1) / (int)gridDim.y;
+  const int r_lo = blockIdx.y * rows_here, r_hi = min(BM, r_lo + rows_here);
+  const size_t tile_elems = (size_t)BM * (size_t)BN;
+  const double *first = partial + (size_t)seg.x * tile_elems;
+  for (int idx = r_lo * words_per_row + threadIdx.x; idx < r_hi * words_per_row; idx += blockDim.x) {
+    const int r = idx / words_per_row, c = (idx - r * words_per_row) << 1;
+    const int row = tile_m * BM + r, col = tile_n * BN + c;
+    if (row >= M || col >= N) continue;
     double2 v = make_double2(0.0, 0.0);
-    for (int s = 0; s < splits; s++) {
-      const double2 p = __ldcs(reinterpret_cast<const double2 *>(partial + (size_t)s * MN) + i);
+    for (int k = 0; k < seg.y; k++) {
+      const double2 p =
+          __ldcs(reinterpret_cast<const double2 *>(first + (size_t)k * tile_elems + (size_t)r * BN + c));
       v.x += p.x;
       v.y += p.y;
     }
-    const size_t at = i * 2;
-    v = apply_epilogue(v, ep, at, (int)(at % (size_t)N));
+    const size_t at = (size_t)row * (size_t)N + (size_t)col;
+    v = apply_epilogue(v, ep, at, col);
     *reinterpret_cast<double2 *>(ep.D + at) = v;
   }
 }
@@ -587,7 +612,10 @@ static int default_dmma_shape() {
 struct DmmaLaunch {
   CUtensorMap ma, mb;
   GemmEpilogue ep;
-  int M, N, K, tiles_m, tiles_n, splits, kt_per_split;
+  int M, N, K, tiles_m, tiles_n;
+  const SegItem *table;  // segments of a split contraction (device), or null: whole tiles
+  int items;             // CTAs' worth of work: segments, or tiles
+  int min_nkt;           // shortest item, in k-tiles
   int grouped_ab;  // bit 0 / bit 1: operand A / B uses the grouped 3-D tensor map
 };
 
@@ -602,18 +630,13 @@ static int launch_dmma_variant(const DmmaLaunch &L) {
     configured = true;
   }
   Context &c = ctx();
-  const int tiles = L.tiles_m * L.tiles_n;
-  // bottom row of tiles less than half full -> its tiles are "light"
-  const int light = ((L.M % Cfg::BM) != 0 && (L.M % Cfg::BM) * 2 < Cfg::BM && L.tiles_m > 1) ? L.tiles_n : 0;
-  const int items = tiles * L.splits;
   // Long items (many k-tiles) are left to the hardware scheduler, one item per
   // CTA: it balances them dynamically.  Short items (skinny or shallow problems)
   // run as a persistent grid, where the cross-item prefetch hides the pipeline
   // fill that would otherwise dominate them.
-  dim3 grid((unsigned)((PERSISTENT && items > c.sm_count) ? c.sm_count : items), 1, 1);
+  dim3 grid((unsigned)((PERSISTENT && L.items > c.sm_count) ? c.sm_count : L.items), 1, 1);
   kernel<<<grid, kGemmThreads, Cfg::SMEM_BYTES, c.stream>>>(L.ma, L.mb, L.ep, L.M, L.N, L.K, L.tiles_n,
-                                                             tiles - light, light, L.splits,
-                                                             L.kt_per_split, L.grouped_ab, items,
+                                                             L.table, L.grouped_ab, L.items,
                                                              c.kernel_status);
   MG_LAUNCH_CHECK("dmma_gemm");
   return MG_OK;
@@ -625,8 +648,9 @@ static int launch_dmma_kernel(const DmmaLaunch &L) {
     const char *v = std::getenv("MG_GEMM_PERSIST");  // diagnostic: 0 never, 1 always
     return v && *v ? std::atoi(v) : -1;
   }();
-  bool persistent = (L.kt_per_split < 32 || Cfg::BN <= 32) &&
-                    L.tiles_m * L.tiles_n * L.splits > ctx().sm_count;
+  // Segments of a split contraction have unequal lengths and rely on the
+  // hardware scheduler's longest-first pairing, so they never run persistently.
+  bool persistent = !L.table && (L.min_nkt < 32 || Cfg::BN <= 32) && L.items > ctx().sm_count;
   if (persist_mode == 0) persistent = false;
   if (persist_mode == 1) persistent = true;
   if (persistent) return launch_dmma_variant<AK, BK_, SHAPE, EDGE, Cfg, true>(L);
@@ -661,34 +685,26 @@ static int launch_layout(int shape, int tile, const DmmaLaunch &L) {
   }
 }
 
-// Number of contraction splits: the smallest count that fills at least 95% of
-// the last wave of CTAs on the device, with at least 16 k-tiles per split.
-static int choose_splits(int tiles, int KT, int sms) {
-  if (tiles >= 4 * sms) return 1;
-  int max_s = KT / 16;
-  if (max_s > 64) max_s = 64;
-  if (max_s < 1) max_s = 1;
-  int best = 1;
-  double best_eff = 0.0;
-  for (int s = 1; s <= max_s; s++) {
-    const int ctas = tiles * s;
-    const int waves = (ctas + sms - 1) / sms;
-    const double eff = (double)ctas / ((double)waves * sms);
-    if (eff > best_eff + 1e-9) {
-      best_eff = eff;
-      best = s;
-    }
-    if (eff >= 0.95) return s;
-  }
-  return best;
+// Number of equal spans the (tile, k-tile) iteration space of a problem is cut
+// into, or 0 to run whole tiles.  Whole tiles are kept when they already fill
+// at least 95% of their last wave of CTAs, or when the contraction is too short
+// to share; otherwise one span per SM, at least 16 k-tiles long.
+static int choose_spans(int tiles, int KT, int sms) {
+  if (tiles >= 4 * sms || KT < 32) return 0;
+  const int waves = (tiles + sms - 1) / sms;
+  if ((double)tiles / ((double)waves * sms) >= 0.95) return 0;
+  long long spans = (long long)tiles * KT / 16;
+  if (spans > sms) spans = sms;
+  return spans > 1 ? (int)spans : 0;
 }
 
 // Tile configuration and contraction split for a problem.  Candidates are
-// costed as (waves of CTAs) x (work per CTA), with a small handicap for the
+// costed as (rounds of CTAs) x (work per CTA), with a small handicap for the
 // half-width tile (more operand traffic per flop) and for a split contraction
-// (its partial tiles are written and folded: ~22.8 (s+1)/K of the GEMM's time).
+// (its partial tiles are written and folded: ~22.8 (p+1)/K of the GEMM's time
+// when p partial tiles are written per output tile).
 struct GemmPlan {
-  int tile, bm, bn, splits;
+  int tile, bm, bn, spans;
 };
 
 static GemmPlan choose_plan(int M, int N, int K, int sms, int shape) {
@@ -696,14 +712,14 @@ static GemmPlan choose_plan(int M, int N, int K, int sms, int shape) {
   auto tiles_of = [&](int bm, int bn) { return ((M + bm - 1) / bm) * ((N + bn - 1) / bn); };
   if (N <= Skinny16Cfg::BN) {
     return {kTileSkinny16, Skinny16Cfg::BM, Skinny16Cfg::BN,
-            choose_splits(tiles_of(Skinny16Cfg::BM, Skinny16Cfg::BN), KT, sms)};
+            choose_spans(tiles_of(Skinny16Cfg::BM, Skinny16Cfg::BN), KT, sms)};
   }
   if (N <= SkinnyCfg::BN) {
     return {kTileSkinny, SkinnyCfg::BM, SkinnyCfg::BN,
-            choose_splits(tiles_of(SkinnyCfg::BM, SkinnyCfg::BN), KT, sms)};
+            choose_spans(tiles_of(SkinnyCfg::BM, SkinnyCfg::BN), KT, sms)};
   }
   GemmPlan main_plan{kTileMain, MainCfg::BM, MainCfg::BN,
-                     choose_splits(tiles_of(MainCfg::BM, MainCfg::BN), KT, sms)};
+                     choose_spans(tiles_of(MainCfg::BM, MainCfg::BN), KT, sms)};
   static const int forced = [] {
     const char *v = std::getenv("MG_GEMM_TILE");  // diagnostic: "main" or "half"
     if (!v) return -1;
@@ -711,24 +727,110 @@ static GemmPlan choose_plan(int M, int N, int K, int sms, int shape) {
   }();
   if (shape != 2 || forced == kTileMain) return main_plan;
   GemmPlan half_plan{kTileHalf, HalfCfg::BM, HalfCfg::BN,
-                     choose_splits(tiles_of(HalfCfg::BM, HalfCfg::BN), KT, sms)};
+                     choose_spans(tiles_of(HalfCfg::BM, HalfCfg::BN), KT, sms)};
   if (forced == kTileHalf) return half_plan;
   auto cost = [&](const GemmPlan &p, double handicap) {
-    const int ctas = tiles_of(p.bm, p.bn) * p.splits;
-    const int waves = (ctas + sms - 1) / sms;
-    const int kt = (KT + p.splits - 1) / p.splits;
-    double c = (double)waves * p.bm * p.bn * kt * handicap;
-    if (p.splits > 1) c *= 1.0 + 22.8 * (p.splits + 1) / (double)K;
-    return c;
+    const int tiles = tiles_of(p.bm, p.bn);
+    if (p.spans == 0) {
+      const int waves = (tiles + sms - 1) / sms;
+      return (double)waves * p.bm * p.bn * KT * handicap;
+    }
+    const double per_cta = (double)tiles * KT / p.spans;
+    const double partials = std::min(2.0 * p.spans, (double)p.spans + tiles) / tiles;
+    return per_cta * p.bm * p.bn * handicap * (1.0 + 22.8 * (partials + 1.0) / (double)K);
   };
   GemmPlan best = cost(half_plan, 1.04) < cost(main_plan, 1.0) ? half_plan : main_plan;
   double best_cost = best.tile == kTileHalf ? cost(half_plan, 1.04) : cost(main_plan, 1.0);
   if (M % MainCfg::BM != 0 && M % Rows112Cfg::BM == 0) {
     GemmPlan p112{kTileRows112, Rows112Cfg::BM, Rows112Cfg::BN,
-                  choose_splits(tiles_of(Rows112Cfg::BM, Rows112Cfg::BN), KT, sms)};
+                  choose_spans(tiles_of(Rows112Cfg::BM, Rows112Cfg::BN), KT, sms)};
     if (cost(p112, 1.02) < best_cost) best = p112;
   }
   return best;
+}
+
+// ---------------------------------------------------------------------------
+// Segment tables of split contractions.  A table depends only on the tile grid,
+// the k-tile count and the span count, so it is built once per shape and kept
+// on the device until shutdown.
+// ---------------------------------------------------------------------------
+struct SegTable {
+  int tiles_m, tiles_n, KT, bm, bn, spans;  // key
+  int items, slots, min_nkt;
+  SegItem *dev_items;  // [items], longest first
+  int2 *dev_tiles;     // [tiles]: (first slot, segment count) or (0, 0) for a tile written directly
+};
+
+static std::vector<SegTable> g_seg_tables;
+
+void gemm_release_tables() {
+  for (auto &t : g_seg_tables) {
+    cudaFree(t.dev_items);
+    cudaFree(t.dev_tiles);
+  }
+  g_seg_tables.clear();
+}
+
+static int seg_table_for(int tiles_m, int tiles_n, int KT, int bm, int bn, int spans,
+                         const SegTable **out) {
+  for (const auto &t : g_seg_tables) {
+    if (t.tiles_m == tiles_m && t.tiles_n == tiles_n && t.KT == KT && t.bm == bm && t.bn == bn &&
+        t.spans == spans) {
+      *out = &t;
+      return MG_OK;
+    }
+  }
+  const int tiles = tiles_m * tiles_n;
+  const long long units = (long long)tiles * KT;
+  std::vector<SegItem> segs;  // in (tile, k) order
+  std::vector<int> per_tile((size_t)tiles, 0);
+  for (int j = 0; j < spans; j++) {
+    long long u = units * j / spans;
+    const long long end = units * (j + 1) / spans;
+    while (u < end) {
+      const int tile = (int)(u / KT);
+      const int kt = (int)(u - (long long)tile * KT);
+      const int n = (int)std::min<long long>(end - u, KT - kt);
+      SegItem it{};
+      it.m0 = (tile / tiles_n) * bm;
+      it.n0 = (tile % tiles_n) * bn;
+      it.kt_begin = kt;
+      it.nkt = n;
+      it.slot = tile;  // provisional: the tile index
+      segs.push_back(it);
+      per_tile[(size_t)tile]++;
+      u += n;
+    }
+  }
+  std::vector<int2> tile_info((size_t)tiles, make_int2(0, 0));
+  int slots = 0, min_nkt = KT;
+  for (auto &it : segs) {
+    const int tile = it.slot;
+    if (per_tile[(size_t)tile] > 1) {
+      if (tile_info[(size_t)tile].y == 0) tile_info[(size_t)tile].x = slots;
+      tile_info[(size_t)tile].y++;
+      it.slot = slots++;
+    } else {
+      it.slot = -1;
+    }
+    min_nkt = std::min(min_nkt, it.nkt);
+  }
+  std::stable_sort(segs.begin(), segs.end(),
+                   [](const SegItem &a, const SegItem &b) { return a.nkt > b.nkt; });
+  SegTable t{};
+  t.tiles_m = tiles_m; t.tiles_n = tiles_n; t.KT = KT; t.bm = bm; t.bn = bn; t.spans = spans;
+  t.items = (int)segs.size();
+  t.slots = slots;
+  t.min_nkt = min_nkt;
+  MG_CUDA_TRY(cudaMalloc(&t.dev_items, segs.size() * sizeof(SegItem)));
+  MG_CUDA_TRY(cudaMalloc(&t.dev_tiles, tile_info.size() * sizeof(int2)));
+  MG_CUDA_TRY(cudaMemcpy(t.dev_items, segs.data(), segs.size() * sizeof(SegItem),
+                         cudaMemcpyHostToDevice));
+  MG_CUDA_TRY(cudaMemcpy(t.dev_tiles, tile_info.data(), tile_info.size() * sizeof(int2),
+                         cudaMemcpyHostToDevice));
+  g_seg_tables.push_back(t);
+  *out = &g_seg_tables.back();
+  return MG_OK;
 }
 
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -810,18 +912,23 @@ static int run_gemm(const GemmDesc &d) {
 
   const int tiles_m = (M + bm - 1) / bm, tiles_n = (N + bn - 1) / bn;
   const int KT = (K + BK - 1) / BK;
-  int splits = plan.splits;
-  int kt_per_split = (KT + splits - 1) / splits;
-  splits = (KT + kt_per_split - 1) / kt_per_split;
-  if (splits > 1) {
-    int rc = ensure_scratch(&c.splitk_scratch, &c.splitk_scratch_elems,
-                            (size_t)splits * d.M * d.N);
+  const SegTable *table = nullptr;
+  if (plan.spans > 0) {
+    int rc = seg_table_for(tiles_m, tiles_n, KT, bm, bn, plan.spans, &table);
     if (rc != MG_OK) return rc;
-    ep.partial = c.splitk_scratch;
+    if (table->slots > 0) {
+      rc = ensure_scratch(&c.splitk_scratch, &c.splitk_scratch_elems,
+                          (size_t)table->slots * (size_t)bm * (size_t)bn);
+      if (rc != MG_OK) return rc;
+      ep.partial = c.splitk_scratch;
+    }
   }
   L.ep = ep;
   L.M = M; L.N = N; L.K = K;
-  L.tiles_m = tiles_m; L.tiles_n = tiles_n; L.splits = splits; L.kt_per_split = kt_per_split;
+  L.tiles_m = tiles_m; L.tiles_n = tiles_n;
+  L.table = table ? table->dev_items : nullptr;
+  L.items = table ? table->items : tiles_m * tiles_n;
+  L.min_nkt = table ? table->min_nkt : KT;
   int rc;
   if (d.a_kcontig && !d.b_kcontig)
     rc = launch_layout<true, false>(shape, plan.tile, L);
@@ -832,12 +939,12 @@ static int run_gemm(const GemmDesc &d) {
   else
     return fail(MG_ERR_INVALID, "gemm: unsupported operand layout");
   if (rc != MG_OK) return rc;
-  if (splits > 1) {
+  if (table && table->slots > 0) {
     GemmEpilogue fin = ep;
     fin.partial = nullptr;
-    const size_t MN = d.M * d.N;
-    splitk_finish_kernel<<<grid_for(MN / 2, 256, 8), 256, 0, c.stream>>>(c.splitk_scratch, splits,
-                                                                         MN, N, fin);
+    dim3 grid((unsigned)(tiles_m * tiles_n), 4, 1);
+    splitk_finish_kernel<<<grid, 256, 0, c.stream>>>(c.splitk_scratch, table->dev_tiles, tiles_n, bm,
+                                                     bn, M, N, fin);
     MG_LAUNCH_CHECK("splitk_finish");
   }
   return MG_OK;

@@ -180,6 +180,34 @@ def test_split_contraction_is_reproducible_and_correct(abi, fast):
     abi.mg_check_kernel_status()
 
 
+@pytest.mark.parametrize("M,Kd,N", [(4096, 784, 200), (6000, 300, 136), (2048, 1024, 10),
+                                     (8192, 200, 1000), (3000, 130, 258)])
+def test_split_contraction_ragged_shapes_bit_exact_on_integers(abi, M, Kd, N):
+    """Long contractions over few output tiles are cut into per-SM spans whose
+    segments cross tile boundaries; partial tiles are packed and folded in k
+    order.  Small-integer operands make every partial sum exact, so the result
+    must equal the integer product bit for bit, including ragged borders, for the
+    weight-gradient (A^T.G), forward (A.B) and input-gradient (G.B^T) layouts."""
+    rng = np.random.default_rng(M + Kd + N)
+    A = rng.integers(-3, 4, (M, Kd)).astype(np.float64)
+    G = rng.integers(-3, 4, (M, N)).astype(np.float64)
+    g0 = rng.integers(-5, 6, (Kd, N)).astype(np.float64)
+    dA, dG, out = abi.array(A), abi.array(G), abi.array(g0)
+    abi.mg_gemm_tn(dA.ptr, dG.ptr, out.ptr, M, N, Kd, 1)          # [Kd, N] += A^T.G, contraction M
+    assert np.array_equal(out.numpy((Kd, N)), g0 + A.T @ G)
+    # forward layout with the long axis as the contraction: [Kd, M].[M, N]
+    At = np.ascontiguousarray(A.T)
+    dAt, C = abi.array(At), abi.empty(Kd * N)
+    abi.mg_gemm_nn(dAt.ptr, dG.ptr, C.ptr, Kd, N, M, 0, K.EPI_NONE, None)
+    assert np.array_equal(C.numpy((Kd, N)), At @ G)
+    # input-gradient layout: [Kd, M].[N, M]^T
+    Gt = np.ascontiguousarray(G.T)
+    dGt, D = abi.array(Gt), abi.array(g0)
+    abi.mg_gemm_nt(dAt.ptr, dGt.ptr, D.ptr, Kd, M, N, 1, K.EPI_NONE, None)
+    assert np.array_equal(D.numpy((Kd, N)), g0 + At @ Gt.T)
+    abi.mg_check_kernel_status()
+
+
 def test_empty_dimensions(abi):
     out = abi.array(np.ones(6))
     abi.mg_gemm_nn(None, None, out.ptr, 2, 3, 0, 0, K.EPI_NONE, None)   # K = 0 -> zeros
