@@ -411,52 +411,65 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         bias[nt] = make_double2(0.0, 0.0);
         if (use_bias && col < N) bias[nt] = make_double2(__ldg(ep.aux + col), __ldg(ep.aux + col + 1));
       }
+      // Small accumulators (128 x 64 tiles and narrower) leave room to fetch the
+      // mask / old values of the whole tile at once: twice the loads in flight,
+      // which is what a one-k-tile problem (the gradient through the 10 logits)
+      // lives on.  Larger ones go 16 rows at a time.
+      constexpr int EG = (MT * NT <= 8) ? MT : 1;
 #pragma unroll
-      for (int mt = 0; mt < MT; mt++) {
-        double2 mask[2][NT], old[2][NT];
+      for (int mt0 = 0; mt0 < MT; mt0 += EG) {
+        double2 mask[EG][2][NT], old[EG][2][NT];
         if (use_mask || use_old) {
 #pragma unroll
-          for (int h = 0; h < 2; h++) {
-            const int row = m0 + wm + mt * 16 + g + 8 * h;
+          for (int e = 0; e < EG; e++) {
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++) {
-              const int col = n0 + wn + nt * 8 + 2 * t;
-              const bool in = row < M && col < N;
-              const size_t at = (size_t)row * (size_t)N + (size_t)col;  // only used when direct
-              mask[h][nt] = (use_mask && in) ? __ldcs(reinterpret_cast<const double2 *>(ep.aux + at))
-                                             : make_double2(0.0, 0.0);
-              old[h][nt] = (use_old && in) ? __ldcs(reinterpret_cast<const double2 *>(ep.D + at))
-                                           : make_double2(0.0, 0.0);
+            for (int h = 0; h < 2; h++) {
+              const int row = m0 + wm + (mt0 + e) * 16 + g + 8 * h;
+#pragma unroll
+              for (int nt = 0; nt < NT; nt++) {
+                const int col = n0 + wn + nt * 8 + 2 * t;
+                const bool in = row < M && col < N;
+                const size_t at = (size_t)row * (size_t)N + (size_t)col;  // only used when direct
+                mask[e][h][nt] = (use_mask && in)
+                                     ? __ldcs(reinterpret_cast<const double2 *>(ep.aux + at))
+                                     : make_double2(0.0, 0.0);
+                old[e][h][nt] = (use_old && in) ? __ldcs(reinterpret_cast<const double2 *>(ep.D + at))
+                                                : make_double2(0.0, 0.0);
+              }
             }
           }
         }
 #pragma unroll
-        for (int h = 0; h < 2; h++) {
-          const int row = m0 + wm + mt * 16 + g + 8 * h;
-          if (row >= row_end) continue;
+        for (int e = 0; e < EG; e++) {
+          const int mt = mt0 + e;
 #pragma unroll
-          for (int nt = 0; nt < NT; nt++) {
-            const int col = n0 + wn + nt * 8 + 2 * t;
-            if (col >= col_end) continue;
-            const size_t at = (size_t)(row - row_base) * ld + (size_t)(col - col_base);
-            double2 v = make_double2(acc[mt][nt][2 * h], acc[mt][nt][2 * h + 1]);
-            if (use_bias) {
-              v.x += bias[nt].x;
-              v.y += bias[nt].y;
-              if (ep.mode == MG_EPI_BIAS_RELU) {
-                v.x = v.x > 0 ? v.x : 0.0;
-                v.y = v.y > 0 ? v.y : 0.0;
+          for (int h = 0; h < 2; h++) {
+            const int row = m0 + wm + mt * 16 + g + 8 * h;
+            if (row >= row_end) continue;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+              const int col = n0 + wn + nt * 8 + 2 * t;
+              if (col >= col_end) continue;
+              const size_t at = (size_t)(row - row_base) * ld + (size_t)(col - col_base);
+              double2 v = make_double2(acc[mt][nt][2 * h], acc[mt][nt][2 * h + 1]);
+              if (use_bias) {
+                v.x += bias[nt].x;
+                v.y += bias[nt].y;
+                if (ep.mode == MG_EPI_BIAS_RELU) {
+                  v.x = v.x > 0 ? v.x : 0.0;
+                  v.y = v.y > 0 ? v.y : 0.0;
+                }
               }
+              if (use_mask) {
+                v.x = v.x * (mask[e][h][nt].x > 0 ? 1.0 : 0.0);
+                v.y = v.y * (mask[e][h][nt].y > 0 ? 1.0 : 0.0);
+              }
+              if (use_old) {
+                v.x = old[e][h][nt].x + v.x;
+                v.y = old[e][h][nt].y + v.y;
+              }
+              *reinterpret_cast<double2 *>(dst + at) = v;
             }
-            if (use_mask) {
-              v.x = v.x * (mask[h][nt].x > 0 ? 1.0 : 0.0);
-              v.y = v.y * (mask[h][nt].y > 0 ? 1.0 : 0.0);
-            }
-            if (use_old) {
-              v.x = old[h][nt].x + v.x;
-              v.y = old[h][nt].y + v.y;
-            }
-            *reinterpret_cast<double2 *>(dst + at) = v;
           }
         }
       }
@@ -729,6 +742,9 @@ static GemmPlan choose_plan(int M, int N, int K, int sms, int shape) {
   GemmPlan half_plan{kTileHalf, HalfCfg::BM, HalfCfg::BN,
                      choose_spans(tiles_of(HalfCfg::BM, HalfCfg::BN), KT, sms)};
   if (forced == kTileHalf) return half_plan;
+  // One k-tile: the problem is all epilogue (a rank-16 update streamed through
+  // HBM); the half-width tile keeps the whole tile's epilogue loads in flight.
+  if (KT == 1) return half_plan;
   auto cost = [&](const GemmPlan &p, double handicap) {
     const int tiles = tiles_of(p.bm, p.bn);
     if (p.spans == 0) {
