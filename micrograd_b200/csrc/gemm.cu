@@ -59,6 +59,13 @@ struct TileCfg {
   static constexpr int A_BYTES = BM * BK * 8, B_BYTES = BN * BK * 8;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 2 * STAGES * 8;
+  // The ReLU-mask source tile of an output tile, staged through the same ring
+  // after the last k-tile: BN/16 boxes of BM rows x 16 columns (128-byte rows).
+  static constexpr int MASK_BOXES = BN / 16, MASK_BOX_BYTES = BM * 128;
+  static constexpr int MASK_BOXES_PER_STAGE = STAGE_BYTES / MASK_BOX_BYTES;
+  static constexpr int MASK_STAGES = (MASK_BOXES + MASK_BOXES_PER_STAGE - 1) / MASK_BOXES_PER_STAGE;
+  static_assert(MASK_BOXES_PER_STAGE >= 1 && MASK_STAGES <= STAGES, "mask tile must fit the ring");
+  static_assert(MASK_BOX_BYTES % 1024 == 0, "swizzled boxes need 1 KB alignment");
   static_assert(A_BYTES % 1024 == 0 && B_BYTES % 1024 == 0, "swizzled tiles need 1 KB alignment");
   static_assert(BM % 16 == 0 && BN % 16 == 0, "tiles are built from 16-wide TMA boxes");
 };
@@ -279,11 +286,15 @@ __device__ __forceinline__ WorkItem decode_work(int id, int tiles_n, int KT,
 // (skinny or shallow problems).  Otherwise every CTA processes exactly one item
 // and the hardware scheduler balances the load; the loop below then compiles to
 // straight-line code, which keeps the consumer's register budget free of spills.
-template <bool A_KCONTIG, bool B_KCONTIG, int SHAPE, bool EDGE, class Cfg, bool PERSISTENT>
+// MASKED: the epilogue is the ReLU mask and its source tile is staged through the
+// ring by the producer (a separate instantiation, so that the other epilogues'
+// register allocation is untouched).
+template <bool A_KCONTIG, bool B_KCONTIG, int SHAPE, bool EDGE, class Cfg, bool PERSISTENT, bool MASKED>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-                 GemmEpilogue ep, int M, int N, int K, int tiles_n,
-                 const SegItem *__restrict__ table, int grouped_ab, int total_items, int *status) {
+                 const __grid_constant__ CUtensorMap mapMask, GemmEpilogue ep, int M, int N, int K,
+                 int tiles_n, const SegItem *__restrict__ table, int grouped_ab, int total_items,
+                 int *status) {
   constexpr int BM = Cfg::BM, BN = Cfg::BN, MT = Cfg::MT, NT = Cfg::NT;
   constexpr int kStages = Cfg::STAGES, kStageBytes = Cfg::STAGE_BYTES, kTileBytes = Cfg::A_BYTES;
   extern __shared__ uint8_t smem_raw[];
@@ -314,6 +325,7 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     if (warp == kConsumerWarps && lane == 0) {
       prefetch_tensormap(&mapA);
       prefetch_tensormap(&mapB);
+      if (MASKED) prefetch_tensormap(&mapMask);
       unsigned ring = 0;  // stages issued by this CTA so far
       bool alive = true;
       int id = blockIdx.x;
@@ -347,6 +359,26 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
           } else {
             for (int b = 0; b < BN / 16; b++)
               tma_load_2d(b_dst + b * 2048, &mapB, w.n0 + 16 * b, k0, bar);
+          }
+        }
+        // The mask source of this tile follows its operands through the ring: the
+        // copies overlap the tile's last MMAs and the epilogue reads shared memory.
+        if (MASKED && w.slot < 0 && alive) {
+          for (int ms = 0; ms < Cfg::MASK_STAGES; ++ms, ++ring) {
+            const unsigned s = ring % kStages;
+            if (ring >= (unsigned)kStages) {
+              if (!mbar_wait_bounded(smem_u32(empty_bar + s), ((ring / kStages) - 1) & 1, abort_flag)) {
+                alive = false;
+                break;
+              }
+            }
+            const uint32_t bar = smem_u32(full_bar + s);
+            const int first = ms * Cfg::MASK_BOXES_PER_STAGE;
+            const int boxes = min(Cfg::MASK_BOXES_PER_STAGE, Cfg::MASK_BOXES - first);
+            mbar_arrive_expect_tx(bar, (uint32_t)(boxes * Cfg::MASK_BOX_BYTES));
+            const uint32_t dst = smem_u32(smem + s * kStageBytes);
+            for (int b = 0; b < boxes; b++)
+              tma_load_2d(dst + b * Cfg::MASK_BOX_BYTES, &mapMask, w.n0 + 16 * (first + b), w.m0, bar);
           }
         }
         if (!PERSISTENT) break;
@@ -385,6 +417,18 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
       const bool ok = consumer_loop<A_KCONTIG, B_KCONTIG, SHAPE, Cfg>(
           acc, smem, full_bar, empty_bar, w.nkt, ring, abort_flag, c0, g, wm, wn, lane, active);
       if (!ok) break;
+      // Mask source staged by the producer: wait for all of its stages (every warp,
+      // also an inactive one, keeps the ring's barrier protocol).
+      const bool mask_smem = MASKED && w.slot < 0;
+      const unsigned mask_ring = ring;
+      bool mask_ok = true;
+      if (mask_smem) {
+        for (int ms = 0; ms < Cfg::MASK_STAGES && mask_ok; ms++) {
+          const unsigned r2 = mask_ring + ms;
+          mask_ok = mbar_wait_bounded(smem_u32(full_bar + r2 % kStages), (r2 / kStages) & 1, abort_flag);
+        }
+        if (!mask_ok) break;
+      }
       if (active) {
 
       // ---------------- epilogue ----------------
@@ -395,15 +439,23 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
       // epilogue into a chain of exposed memory latencies.
       // A segment of a split tile stores its whole BM x BN accumulator, packed,
       // into its slot of the scratch buffer (rows and columns beyond the matrix
-      // hold zeros or are never read); everything else goes to D with bounds.
-      const bool direct = w.slot < 0;
-      double *dst = direct ? ep.D : ep.partial + (size_t)w.slot * (size_t)(BM * BN);
-      const size_t ld = direct ? (size_t)N : (size_t)BN;
-      const int row_base = direct ? 0 : m0, col_base = direct ? 0 : n0;
-      const int row_end = direct ? M : m0 + BM, col_end = direct ? N : n0 + BN;
-      const bool use_mask = direct && ep.mode == MG_EPI_RELU_MASK;
-      const bool use_bias = direct && (ep.mode == MG_EPI_BIAS || ep.mode == MG_EPI_BIAS_RELU);
-      const bool use_old = direct && ep.accumulate;
+      // hold zeros or are never read) and is done.  This is a branch of its own so
+      // that the final epilogue below keeps its register allocation.
+      if (w.slot >= 0) {
+        double *slot = ep.partial + (size_t)w.slot * (size_t)(BM * BN);
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+          for (int h = 0; h < 2; h++)
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++)
+              *reinterpret_cast<double2 *>(slot + (wm + mt * 16 + g + 8 * h) * BN + wn + nt * 8 + 2 * t) =
+                  make_double2(acc[mt][nt][2 * h], acc[mt][nt][2 * h + 1]);
+      } else {
+      double *dst = ep.D;
+      const bool use_mask = ep.mode == MG_EPI_RELU_MASK;
+      const bool use_bias = !MASKED && (ep.mode == MG_EPI_BIAS || ep.mode == MG_EPI_BIAS_RELU);
+      const bool use_old = ep.accumulate != 0;
       double2 bias[NT];
 #pragma unroll
       for (int nt = 0; nt < NT; nt++) {
@@ -429,10 +481,20 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
               for (int nt = 0; nt < NT; nt++) {
                 const int col = n0 + wn + nt * 8 + 2 * t;
                 const bool in = row < M && col < N;
-                const size_t at = (size_t)row * (size_t)N + (size_t)col;  // only used when direct
-                mask[e][h][nt] = (use_mask && in)
-                                     ? __ldcs(reinterpret_cast<const double2 *>(ep.aux + at))
-                                     : make_double2(0.0, 0.0);
+                const size_t at = (size_t)row * (size_t)N + (size_t)col;
+                if (mask_smem) {
+                  // box = 16-column group of the tile, 128-byte rows, 16-byte chunks
+                  // XOR-swizzled with the row; out-of-range elements were zero-filled.
+                  const int r = row - m0, cc = col - n0, box = cc >> 4, chunk = (cc & 15) >> 1;
+                  const unsigned st = (mask_ring + box / Cfg::MASK_BOXES_PER_STAGE) % kStages;
+                  mask[e][h][nt] = *reinterpret_cast<const double2 *>(
+                      smem + st * kStageBytes + (box % Cfg::MASK_BOXES_PER_STAGE) * Cfg::MASK_BOX_BYTES +
+                      r * 128 + ((chunk ^ (r & 7)) << 4));
+                } else {
+                  mask[e][h][nt] = (use_mask && in)
+                                       ? __ldcs(reinterpret_cast<const double2 *>(ep.aux + at))
+                                       : make_double2(0.0, 0.0);
+                }
                 old[e][h][nt] = (use_old && in) ? __ldcs(reinterpret_cast<const double2 *>(ep.D + at))
                                                 : make_double2(0.0, 0.0);
               }
@@ -445,12 +507,12 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
 #pragma unroll
           for (int h = 0; h < 2; h++) {
             const int row = m0 + wm + mt * 16 + g + 8 * h;
-            if (row >= row_end) continue;
+            if (row >= M) continue;
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
               const int col = n0 + wn + nt * 8 + 2 * t;
-              if (col >= col_end) continue;
-              const size_t at = (size_t)(row - row_base) * ld + (size_t)(col - col_base);
+              if (col >= N) continue;
+              const size_t at = (size_t)row * (size_t)N + (size_t)col;
               double2 v = make_double2(acc[mt][nt][2 * h], acc[mt][nt][2 * h + 1]);
               if (use_bias) {
                 v.x += bias[nt].x;
@@ -473,7 +535,15 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
           }
         }
       }
+      }  // final epilogue
       }  // active
+      if (mask_smem) {
+        __syncwarp();
+        if (lane == 0)
+          for (int ms = 0; ms < Cfg::MASK_STAGES; ms++)
+            mbar_arrive(smem_u32(empty_bar + (mask_ring + ms) % kStages));
+        ring += Cfg::MASK_STAGES;
+      }
       if (!PERSISTENT) break;
       id += gridDim.x;
     } while (id < total_items);
@@ -623,7 +693,8 @@ static int default_dmma_shape() {
 }
 
 struct DmmaLaunch {
-  CUtensorMap ma, mb;
+  CUtensorMap ma, mb, mmask;
+  int mask_tma;  // mmask describes the ReLU-mask source; the producer stages it
   GemmEpilogue ep;
   int M, N, K, tiles_m, tiles_n;
   const SegItem *table;  // segments of a split contraction (device), or null: whole tiles
@@ -633,10 +704,10 @@ struct DmmaLaunch {
 };
 
 
-template <bool AK, bool BK_, int SHAPE, bool EDGE, class Cfg, bool PERSISTENT>
-static int launch_dmma_variant(const DmmaLaunch &L) {
+template <bool AK, bool BK_, int SHAPE, bool EDGE, class Cfg, bool PERSISTENT, bool MASKED>
+static int launch_dmma_masked(const DmmaLaunch &L) {
   static bool configured = false;
-  auto kernel = dmma_gemm_kernel<AK, BK_, SHAPE, EDGE, Cfg, PERSISTENT>;
+  auto kernel = dmma_gemm_kernel<AK, BK_, SHAPE, EDGE, Cfg, PERSISTENT, MASKED>;
   if (!configured) {
     MG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      Cfg::SMEM_BYTES));
@@ -648,11 +719,21 @@ static int launch_dmma_variant(const DmmaLaunch &L) {
   // run as a persistent grid, where the cross-item prefetch hides the pipeline
   // fill that would otherwise dominate them.
   dim3 grid((unsigned)((PERSISTENT && L.items > c.sm_count) ? c.sm_count : L.items), 1, 1);
-  kernel<<<grid, kGemmThreads, Cfg::SMEM_BYTES, c.stream>>>(L.ma, L.mb, L.ep, L.M, L.N, L.K, L.tiles_n,
-                                                             L.table, L.grouped_ab, L.items,
-                                                             c.kernel_status);
+  kernel<<<grid, kGemmThreads, Cfg::SMEM_BYTES, c.stream>>>(L.ma, L.mb, L.mmask, L.ep, L.M, L.N, L.K,
+                                                             L.tiles_n, L.table, L.grouped_ab,
+                                                             L.items, c.kernel_status);
   MG_LAUNCH_CHECK("dmma_gemm");
   return MG_OK;
+}
+
+// The staged-mask instantiation exists for the default mma shape and the layout
+// of the input-gradient product (both operands k-contiguous), its only user.
+template <bool AK, bool BK_, int SHAPE, bool EDGE, class Cfg, bool PERSISTENT>
+static int launch_dmma_variant(const DmmaLaunch &L) {
+  if constexpr (AK && BK_ && SHAPE == 2) {
+    if (L.mask_tma) return launch_dmma_masked<AK, BK_, SHAPE, EDGE, Cfg, PERSISTENT, true>(L);
+  }
+  return launch_dmma_masked<AK, BK_, SHAPE, EDGE, Cfg, PERSISTENT, false>(L);
 }
 
 template <bool AK, bool BK_, int SHAPE, bool EDGE, class Cfg>
@@ -745,15 +826,25 @@ static GemmPlan choose_plan(int M, int N, int K, int sms, int shape) {
   // One k-tile: the problem is all epilogue (a rank-16 update streamed through
   // HBM); the half-width tile keeps the whole tile's epilogue loads in flight.
   if (KT == 1) return half_plan;
+  // Every CTA also pays about 3.3 us of launch, pipeline fill and epilogue that
+  // nothing overlaps: 25 800 in the cost's units (bm x bn x k-tiles).
+  constexpr double kPerCta = 25800.0;
   auto cost = [&](const GemmPlan &p, double handicap) {
     const int tiles = tiles_of(p.bm, p.bn);
     if (p.spans == 0) {
       const int waves = (tiles + sms - 1) / sms;
-      return (double)waves * p.bm * p.bn * KT * handicap;
+      return (double)waves * ((double)p.bm * p.bn * KT * handicap + kPerCta);
     }
     const double per_cta = (double)tiles * KT / p.spans;
+    const double segments = (double)tiles / p.spans + 1.0;
     const double partials = std::min(2.0 * p.spans, (double)p.spans + tiles) / tiles;
-    return per_cta * p.bm * p.bn * handicap * (1.0 + 22.8 * (partials + 1.0) / (double)K);
+    double c = (per_cta * p.bm * p.bn * handicap + segments * kPerCta) *
+               (1.0 + 22.8 * (partials + 1.0) / (double)K);
+    // With more tiles than SMs most segments are whole tiles and the cut ones
+    // lose the L2 sharing of a wave that walks k in step: measured 2 % behind
+    // the half-width tile where the model calls it even.
+    if (tiles >= sms) c *= 1.04;
+    return c;
   };
   GemmPlan best = cost(half_plan, 1.04) < cost(main_plan, 1.0) ? half_plan : main_plan;
   double best_cost = best.tile == kTileHalf ? cost(half_plan, 1.04) : cost(main_plan, 1.0);
@@ -925,6 +1016,12 @@ static int run_gemm(const GemmDesc &d) {
     ok_b = make_tensor_map_f64(&L.mb, d.B, d.K, d.N, 16, BK);
   }
   if (!ok_a || !ok_b) return fail(MG_ERR_CUDA, "gemm: cuTensorMapEncodeTiled failed");
+  // ReLU-mask source [M][N]: boxes of bm rows x 16 columns.  If the map cannot be
+  // built the epilogue reads the mask with plain loads instead.
+  L.mmask = L.ma;
+  L.mask_tma = (d.mode == MG_EPI_RELU_MASK && d.a_kcontig && d.b_kcontig && shape == 2 &&
+                make_tensor_map_f64(&L.mmask, d.aux, d.M, d.N, 16, bm))
+                   ? 1 : 0;
 
   const int tiles_m = (M + bm - 1) / bm, tiles_n = (N + bn - 1) / bn;
   const int KT = (K + BK - 1) / BK;
