@@ -157,6 +157,15 @@ int mg_gemm_nt(const double *G, const double *B, double *dA, size_t M, size_t N,
 int mg_gemm_tn(const double *A, const double *G, double *dB, size_t M, size_t N, size_t K,
                int accumulate);
 
+/* Host-only view of the dispatcher's decision for an M x N output with a
+ * contraction of K on a device with sm_count SMs (no device is touched; no
+ * counterpart in the reference).  plan5 = {tile rows, tile columns, spans (0 =
+ * whole tiles), work items, packed partial tiles}.  With spans > 0 and segments
+ * != NULL, segments receives 5 ints per work item in issue order: first row,
+ * first column, first k-tile (16 deep), k-tile count, partial-tile slot (-1 = the
+ * segment covers its tile's whole contraction and runs the final epilogue). */
+int mg_gemm_plan_describe(size_t M, size_t N, size_t K, int sm_count, int *plan5, int *segments,
+                          int max_segments);
 /* Diagnostic knob for tests and benchmarks.  path: 0 automatic choice, 1 plain
  * tiled kernel only, 2 tensor-core kernel whenever the operands allow it.
  * dmma_shape: -1 default, else the mma.sync f64 shape as in

@@ -81,6 +81,8 @@ SIGNATURES = {
     "mg_event_elapsed_ms": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_float)]),
     "mg_event_destroy": (C.c_int, [C.c_int]),
     "mg_event_wait_bounded": (C.c_int, [C.c_int, C.c_double]),
+    "mg_gemm_plan_describe": (C.c_int, [_sz, _sz, _sz, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int),
+                                        C.c_int]),
     "mg_comm_unique_id": (C.c_int, [C.c_char_p]),
     "mg_comm_init": (C.c_int, [C.c_char_p, C.c_int, C.c_int]),
     "mg_comm_destroy": (C.c_int, []),

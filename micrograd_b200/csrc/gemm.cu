@@ -6,8 +6,9 @@
 //     with setmaxnreg); a ring of stages filled by cp.async.bulk.tensor and handed
 //     over through full/empty mbarriers.  Tile configurations (TileCfg): 128 x 128
 //     (2 x 4 warps of 64 x 32) for the compute-bound shapes, 128 x 64 when that
-//     fills the last wave of CTAs better, 128 x 32 for outputs at most 32 columns
-//     wide, 112 x 128 for row counts that are multiples of 112 but not of 128.
+//     fills the last wave of CTAs better or the contraction is a single k-tile,
+//     128 x 32 and 128 x 16 for outputs at most that many columns wide, 112 x 128
+//     for row counts that are multiples of 112 but not of 128.
 //   - Operands land in shared memory in the 128-byte swizzle.  With the k index
 //     of a 16-deep slab permuted (the same permutation for A and B, so the sum is
 //     unchanged) every fragment load is free of bank conflicts: a thread reads
@@ -17,7 +18,9 @@
 //        mn-contiguous tile [16-col group][k][16 cols] : 8-byte loads
 //   - The accumulators stay in registers (FP64 MMA has no TMEM form); the
 //     epilogue adds the bias, applies ReLU or the ReLU mask, and stores or
-//     accumulates 16 bytes per thread per row, all loads before the stores.
+//     accumulates 16 bytes per thread per row, all loads before the stores.  The
+//     mask source tile of the input-gradient product follows the operands
+//     through the TMA ring, so its copy overlaps the tile's last MMAs.
 //   - When the output has too few tiles to fill 148 SMs (weight gradients: the
 //     contraction runs over the batch), the (tile, k-tile) iteration space is cut
 //     into one equal span per SM; a span that crosses a tile boundary becomes two
@@ -878,18 +881,16 @@ void gemm_release_tables() {
   g_seg_tables.clear();
 }
 
-static int seg_table_for(int tiles_m, int tiles_n, int KT, int bm, int bn, int spans,
-                         const SegTable **out) {
-  for (const auto &t : g_seg_tables) {
-    if (t.tiles_m == tiles_m && t.tiles_n == tiles_n && t.KT == KT && t.bm == bm && t.bn == bn &&
-        t.spans == spans) {
-      *out = &t;
-      return MG_OK;
-    }
-  }
+// Host-only construction of a segment table: `segs` in issue order (longest
+// first), `tile_info[t]` = (first slot, segment count) of every tile covered by
+// more than one segment, (0, 0) otherwise.  Slots number the segments of split
+// tiles in (tile, k) order, so a tile's partial tiles are consecutive and in k order.
+static void build_segments(int tiles_m, int tiles_n, int KT, int bm, int bn, int spans,
+                           std::vector<SegItem> &segs, std::vector<int2> &tile_info, int &slots,
+                           int &min_nkt) {
   const int tiles = tiles_m * tiles_n;
   const long long units = (long long)tiles * KT;
-  std::vector<SegItem> segs;  // in (tile, k) order
+  segs.clear();
   std::vector<int> per_tile((size_t)tiles, 0);
   for (int j = 0; j < spans; j++) {
     long long u = units * j / spans;
@@ -909,8 +910,9 @@ static int seg_table_for(int tiles_m, int tiles_n, int KT, int bm, int bn, int s
       u += n;
     }
   }
-  std::vector<int2> tile_info((size_t)tiles, make_int2(0, 0));
-  int slots = 0, min_nkt = KT;
+  tile_info.assign((size_t)tiles, make_int2(0, 0));
+  slots = 0;
+  min_nkt = KT;
   for (auto &it : segs) {
     const int tile = it.slot;
     if (per_tile[(size_t)tile] > 1) {
@@ -924,6 +926,21 @@ static int seg_table_for(int tiles_m, int tiles_n, int KT, int bm, int bn, int s
   }
   std::stable_sort(segs.begin(), segs.end(),
                    [](const SegItem &a, const SegItem &b) { return a.nkt > b.nkt; });
+}
+
+static int seg_table_for(int tiles_m, int tiles_n, int KT, int bm, int bn, int spans,
+                         const SegTable **out) {
+  for (const auto &t : g_seg_tables) {
+    if (t.tiles_m == tiles_m && t.tiles_n == tiles_n && t.KT == KT && t.bm == bm && t.bn == bn &&
+        t.spans == spans) {
+      *out = &t;
+      return MG_OK;
+    }
+  }
+  std::vector<SegItem> segs;
+  std::vector<int2> tile_info;
+  int slots = 0, min_nkt = KT;
+  build_segments(tiles_m, tiles_n, KT, bm, bn, spans, segs, tile_info, slots, min_nkt);
   SegTable t{};
   t.tiles_m = tiles_m; t.tiles_n = tiles_n; t.KT = KT; t.bm = bm; t.bn = bn; t.spans = spans;
   t.items = (int)segs.size();
@@ -1068,6 +1085,41 @@ static int run_gemm(const GemmDesc &d) {
 using namespace mg;
 
 extern "C" {
+
+int mg_gemm_plan_describe(size_t M, size_t N, size_t K, int sm_count, int *plan5, int *segments,
+                          int max_segments) {
+  if (!plan5 || M == 0 || N == 0 || K == 0 || sm_count < 1 || M >= ((size_t)1 << 30) ||
+      N >= ((size_t)1 << 30) || K >= ((size_t)1 << 30))
+    return fail(MG_ERR_INVALID, "mg_gemm_plan_describe: bad arguments");
+  const GemmPlan plan = choose_plan((int)M, (int)N, (int)K, sm_count, 2);
+  const int tiles_m = ((int)M + plan.bm - 1) / plan.bm, tiles_n = ((int)N + plan.bn - 1) / plan.bn;
+  const int KT = ((int)K + BK - 1) / BK;
+  plan5[0] = plan.bm;
+  plan5[1] = plan.bn;
+  plan5[2] = plan.spans;
+  plan5[3] = tiles_m * tiles_n;
+  plan5[4] = 0;
+  if (plan.spans == 0) return MG_OK;
+  std::vector<SegItem> segs;
+  std::vector<int2> tile_info;
+  int slots = 0, min_nkt = 0;
+  build_segments(tiles_m, tiles_n, KT, plan.bm, plan.bn, plan.spans, segs, tile_info, slots, min_nkt);
+  plan5[3] = (int)segs.size();
+  plan5[4] = slots;
+  if (segments) {
+    if ((int)segs.size() > max_segments)
+      return fail(MG_ERR_INVALID, "mg_gemm_plan_describe: %zu segments, room for %d", segs.size(),
+                  max_segments);
+    for (size_t i = 0; i < segs.size(); i++) {
+      segments[5 * i + 0] = segs[i].m0;
+      segments[5 * i + 1] = segs[i].n0;
+      segments[5 * i + 2] = segs[i].kt_begin;
+      segments[5 * i + 3] = segs[i].nkt;
+      segments[5 * i + 4] = segs[i].slot;
+    }
+  }
+  return MG_OK;
+}
 
 int mg_gemm_config(int path, int dmma_shape) {
   if (path < 0 || path > 2) return fail(MG_ERR_INVALID, "mg_gemm_config: path must be 0, 1 or 2");
