@@ -399,7 +399,7 @@ def gemm_roofline(abi, K, rows):
             # profiles/dmma_gemm_kernel_c4_batch32768.md (277.1 + 233.9 MB at 32768 rows), scaled by
             # the rows of this launch: traffic grows in proportion to the batch, the 8 MB weight
             # operand stays L2-resident.
-            "traffic": 511.05e6 * M / 32768.0,
+            "traffic": 510.1e6 * M / 32768.0,
             "traffic_algorithmic": 8.0 * (M * Kd + Kd * N + M * N),
             "traffic_source": "ncu capture at batch 32768, scaled by rows"}
 
