@@ -5,7 +5,8 @@ The product is two shared libraries built in-tree by ``micrograd_b200.build``:
 
 * ``lib/libmg_cuda.so`` — hand-written CUDA kernels behind the C ABI declared in
   ``include/mg_cuda.h`` (device-resident fp64 storage, elementwise / broadcast /
-  reduction / GEMM / fused-loss / SGD kernels, NCCL gradient all-reduce);
+  reduction / GEMM / fused-loss / SGD kernels, gradient all-reduce over peer
+  memory or NCCL);
 * ``lib/libmicrograd.so`` — the C++ ``Tensor``/``Linear``/``SGD`` classes
   (``include/micrograd/*.h``) as a thin graph-building layer over that ABI, plus
   the flat C binding ``include/mg_tensor_c.h``.

@@ -1,7 +1,7 @@
 """Host-side plumbing for minibatch-sharded (data-parallel) runs: one process
 per GPU, launched by ``torch.distributed.run``.
 
-The gradient exchange itself happens inside the library (NCCL all-reduce on its
+The gradient exchange itself happens inside the library (peer-memory or NCCL all-reduce on its
 own stream, started from backward()).  ``torch.distributed`` is only the
 rendezvous: it carries the 128-byte NCCL id from rank 0 to the others, provides
 the barrier around timed regions and the max-over-ranks of a timing.

@@ -1,4 +1,5 @@
-"""GPU: minibatch-sharded training on 2 GPUs of one node (NCCL over NVLink).
+"""GPU: minibatch-sharded training on 2 GPUs of one node (gradient sums over
+NVLink: the library's peer-memory all-reduce kernel, NCCL for plain buffers).
 
 Needs at least two visible GPUs; on a single-GPU machine the test is skipped
 (the host-side logic of the same path is covered on CPU by test_dist_cpu.py
