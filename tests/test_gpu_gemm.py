@@ -208,6 +208,48 @@ def test_split_contraction_ragged_shapes_bit_exact_on_integers(abi, M, Kd, N):
     abi.mg_check_kernel_status()
 
 
+def _boundary_shapes():
+    """Seeded draw of shapes around the tile, k-tile and split boundaries."""
+    rng = np.random.default_rng(2024)
+    ms = [2, 16, 64, 112, 114, 126, 128, 130, 224, 256, 300, 784, 1000, 2048, 4098]
+    ns = [2, 8, 10, 16, 18, 32, 34, 64, 66, 128, 130, 200, 258, 1024]
+    ks = [2, 10, 16, 18, 32, 100, 512, 1000, 2048, 4098, 9000]
+    out = []
+    for _ in range(40):
+        out.append((int(rng.choice(ms)), int(rng.choice(ks)), int(rng.choice(ns))))
+    return sorted(set(out))
+
+
+@pytest.mark.parametrize("M,Kd,N", _boundary_shapes())
+def test_boundary_shapes_with_epilogues_bit_exact_on_integers(abi, M, Kd, N):
+    """Integer operands, tensor-core path wherever the operands allow it: the three
+    products with their fused epilogues (bias+ReLU; ReLU mask with accumulation;
+    accumulation) must equal the integer results exactly for shapes that sit on and
+    around tile edges, single k-tiles, narrow outputs and split contractions."""
+    abi.mg_gemm_config(2, -1)
+    rng = np.random.default_rng(M * 7919 + Kd * 31 + N)
+    A = rng.integers(-3, 4, (M, Kd)).astype(np.float64)
+    B = rng.integers(-3, 4, (Kd, N)).astype(np.float64)
+    G = rng.integers(-3, 4, (M, N)).astype(np.float64)
+    bias = rng.integers(-4, 5, N).astype(np.float64)
+    Hmask = rng.integers(-1, 2, (M, Kd)).astype(np.float64)      # mask source for dA: (> 0)
+    gA0 = rng.integers(-5, 6, (M, Kd)).astype(np.float64)
+    gB0 = rng.integers(-5, 6, (Kd, N)).astype(np.float64)
+    dA, dB, dG, dbias, dH = abi.array(A), abi.array(B), abi.array(G), abi.array(bias), abi.array(Hmask)
+    C = abi.empty(M * N)
+    abi.mg_gemm_nn(dA.ptr, dB.ptr, C.ptr, M, N, Kd, 0, K.EPI_BIAS_RELU, dbias.ptr)
+    assert np.array_equal(C.numpy((M, N)), np.maximum(A @ B + bias, 0.0))
+    dgA, dgB = abi.array(gA0), abi.array(gB0)
+    abi.mg_gemm_nt(dG.ptr, dB.ptr, dgA.ptr, M, N, Kd, 1, K.EPI_RELU_MASK, dH.ptr)
+    assert np.array_equal(dgA.numpy((M, Kd)), gA0 + (G @ B.T) * (Hmask > 0))
+    store = abi.empty(M * Kd)
+    abi.mg_gemm_nt(dG.ptr, dB.ptr, store.ptr, M, N, Kd, 0, K.EPI_RELU_MASK, dH.ptr)
+    assert np.array_equal(store.numpy((M, Kd)), (G @ B.T) * (Hmask > 0))
+    abi.mg_gemm_tn(dA.ptr, dG.ptr, dgB.ptr, M, N, Kd, 1)
+    assert np.array_equal(dgB.numpy((Kd, N)), gB0 + A.T @ G)
+    abi.mg_check_kernel_status()
+
+
 def test_empty_dimensions(abi):
     out = abi.array(np.ones(6))
     abi.mg_gemm_nn(None, None, out.ptr, 2, 3, 0, 0, K.EPI_NONE, None)   # K = 0 -> zeros
