@@ -937,6 +937,10 @@ static int seg_table_for(int tiles_m, int tiles_n, int KT, int bm, int bn, int s
       return MG_OK;
     }
   }
+  // A job with ever-changing shapes (e.g. a varying batch) would grow the cache
+  // without bound: start over beyond 256 tables (cudaFree waits for the kernels
+  // that still read them).
+  if (g_seg_tables.size() >= 256) gemm_release_tables();
   std::vector<SegItem> segs;
   std::vector<int2> tile_info;
   int slots = 0, min_nkt = KT;

@@ -250,6 +250,23 @@ def test_boundary_shapes_with_epilogues_bit_exact_on_integers(abi, M, Kd, N):
     abi.mg_check_kernel_status()
 
 
+def test_many_distinct_split_shapes_recycle_the_table_cache(abi):
+    """A contraction length that changes on every call (a varying batch) builds a
+    new segment table each time; the cache starts over past 256 tables and results
+    stay exact before and after."""
+    rng = np.random.default_rng(5)
+    Kd, N = 128, 128
+    for i in range(300):
+        M = 512 + 16 * i
+        A = rng.integers(-2, 3, (M, Kd)).astype(np.float64)
+        G = rng.integers(-2, 3, (M, N)).astype(np.float64)
+        dA, dG, out = abi.array(A), abi.array(G), abi.empty(Kd * N)
+        abi.mg_gemm_tn(dA.ptr, dG.ptr, out.ptr, M, N, Kd, 0)
+        if i % 37 == 0 or i >= 296:
+            assert np.array_equal(out.numpy((Kd, N)), A.T @ G)
+    abi.mg_check_kernel_status()
+
+
 def test_empty_dimensions(abi):
     out = abi.array(np.ones(6))
     abi.mg_gemm_nn(None, None, out.ptr, 2, 3, 0, 0, K.EPI_NONE, None)   # K = 0 -> zeros
