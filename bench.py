@@ -407,9 +407,10 @@ def gemm_roofline(abi, K, rows):
 def metric_sweeps(abi, K, small=False):
     """The other two parts of the headline metric, measured on one GPU with events:
     DGEMM TFLOP/s (forward C = A.B; benchmark config 3 shapes) and elementwise /
-    reduction GB/s (benchmark config 2 ops at 2^24 and 2^28 elements, algorithmic
-    bytes per element: binary forward 24, unary forward 16, sums 8).  Arrays are
-    far larger than L2 at both sizes."""
+    reduction GB/s (benchmark config 2 ops, forward and backward, at 2^24 and 2^28
+    elements; algorithmic bytes per element: binary forward 24, unary forward 16,
+    sums 8, backward passes as listed below).  Arrays are larger than L2 at both
+    sizes."""
     rng = np.random.default_rng(11)
     seed = abi.array(rng.standard_normal(1 << 22))
 
@@ -435,7 +436,7 @@ def metric_sweeps(abi, K, small=False):
         del a, b, c
     for log2n in ((24, 26) if small else (24, 28)):
         n = 1 << log2n
-        a, b, g, o = filled(n), filled(n), filled(n), abi.empty(n)
+        a, b, g, o, o2 = filled(n), filled(n), filled(n), filled(n), filled(n)
         side = 1 << (log2n // 2)
         ops = (("add", lambda: abi.mg_binary_fwd(K.ADD, a.ptr, b.ptr, o.ptr, n), 24),
                ("mul", lambda: abi.mg_binary_fwd(K.MUL, a.ptr, b.ptr, o.ptr, n), 24),
@@ -447,11 +448,22 @@ def metric_sweeps(abi, K, small=False):
                ("sum", lambda: abi.mg_sum_all_fwd(a.ptr, o.ptr, n), 8),
                ("sum_lastaxis", lambda: abi.mg_sum_lastaxis_fwd(a.ptr, o.ptr, side, side), 8),
                ("mul_bwd_one_side", lambda: abi.mg_binary_bwd(K.MUL, a.ptr, b.ptr, g.ptr, o.ptr, None,
-                                                               n, 0), 40))
+                                                               n, 0), 40),
+               # backward passes, accumulating into existing gradients (read-modify-write):
+               # add 40 B/element (g; ga, gb), mul 56 (g, a, b; ga, gb), unary 32 (g, x or y; gx),
+               # row broadcast 24 (g; gx) + the [N] row gradient, sums 16 (gx)
+               ("add_bwd", lambda: abi.mg_binary_bwd(K.ADD, a.ptr, b.ptr, g.ptr, o.ptr, o2.ptr, n, 0), 40),
+               ("mul_bwd", lambda: abi.mg_binary_bwd(K.MUL, a.ptr, b.ptr, g.ptr, o.ptr, o2.ptr, n, 0), 56),
+               ("relu_bwd", lambda: abi.mg_unary_bwd(K.RELU, a.ptr, b.ptr, 0.0, g.ptr, o.ptr, n, 0), 32),
+               ("tanh_bwd", lambda: abi.mg_unary_bwd(K.TANH, a.ptr, b.ptr, 0.0, g.ptr, o.ptr, n, 0), 32),
+               ("exp_bwd", lambda: abi.mg_unary_bwd(K.EXP, a.ptr, b.ptr, 0.0, g.ptr, o.ptr, n, 0), 32),
+               ("add_row_bwd", lambda: abi.mg_add_row_bwd(g.ptr, o.ptr, o2.ptr, side, side, 0), 24),
+               ("sum_bwd", lambda: abi.mg_sum_all_bwd(g.ptr, o.ptr, n, 0), 16),
+               ("sum_lastaxis_bwd", lambda: abi.mg_sum_lastaxis_bwd(g.ptr, o.ptr, side, side, 0), 16))
         for name, fn, bytes_per in ops:
             ms = timed(fn, 5)
             out["elementwise_gbs"][f"{name}@2^{log2n}"] = round(bytes_per * n / ms / 1e6, 1)
-        del a, b, g, o
+        del a, b, g, o, o2
     return out
 
 
