@@ -425,7 +425,7 @@ def metric_sweeps(abi, K, small=False):
             fn()
         return abi.timed_ms(fn, reps) / reps
 
-    out = {"dgemm_tflops": {}, "elementwise_gbs": {}}
+    out = {"dgemm_tflops": {}, "dgemm_fwd_bwd_tflops": {}, "elementwise_gbs": {}}
     gemm_cases = (("1024^3", (1024, 1024, 1024), 20), ("4096^3", (4096, 4096, 4096), 3),
                   ("8192^3", (8192, 8192, 8192), 2), ("65536x784.784x1024", (65536, 1024, 784), 3))
     # small=True: the 2^24 / 2^26 elementwise cases only (what a profiler capture needs)
@@ -433,7 +433,17 @@ def metric_sweeps(abi, K, small=False):
         a, b, c = filled(m * k), filled(k * n), abi.empty(m * n)
         ms = timed(lambda: abi.mg_gemm_nn(a.ptr, b.ptr, c.ptr, m, n, k, 0, K.EPI_NONE, None), reps)
         out["dgemm_tflops"][tag] = round(2.0 * m * n * k / ms / 1e9, 2)
-        del a, b, c
+        # forward plus both gradients (dA += G.B^T, dB += A^T.G; G = dC), 6 M N K flop
+        g, da, db = filled(m * n), filled(m * k), filled(k * n)
+
+        def fwd_bwd():
+            abi.mg_gemm_nn(a.ptr, b.ptr, c.ptr, m, n, k, 0, K.EPI_NONE, None)
+            abi.mg_gemm_nt(g.ptr, b.ptr, da.ptr, m, n, k, 1, K.EPI_NONE, None)
+            abi.mg_gemm_tn(a.ptr, g.ptr, db.ptr, m, n, k, 1)
+
+        ms = timed(fwd_bwd, max(1, reps // 2))
+        out["dgemm_fwd_bwd_tflops"][tag] = round(6.0 * m * n * k / ms / 1e9, 2)
+        del a, b, c, g, da, db
     for log2n in ((24, 26) if small else (24, 28)):
         n = 1 << log2n
         a, b, g, o, o2 = filled(n), filled(n), filled(n), filled(n), filled(n)

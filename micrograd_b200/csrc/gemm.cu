@@ -91,6 +91,9 @@ using HalfCfg = TileCfg<2, 2, 4, 8>;
 // (784 = 7 x 112, the MNIST-sized input layer's weight gradient), where 128-row
 // tiles would spend an eighth of the machine on padding.
 using Rows112Cfg = TileCfg<8, 7, 2, 6>;
+// 128 x 112, seven 30 KB stages: the same for column counts (the gradient with
+// respect to a 784-wide input): 4 x 2 warps of 32 x 56.
+using Cols112Cfg = TileCfg<2, 2, 7, 7>;
 
 struct GemmEpilogue {
   double *D;            // output [M][N]
@@ -763,7 +766,9 @@ static int launch_tiles(const DmmaLaunch &L) {
   return launch_dmma_kernel<AK, BK_, SHAPE, false, Cfg>(L);
 }
 
-enum TileChoice { kTileMain = 0, kTileSkinny = 1, kTileHalf = 2, kTileRows112 = 3, kTileSkinny16 = 4 };
+enum TileChoice {
+  kTileMain = 0, kTileSkinny = 1, kTileHalf = 2, kTileRows112 = 3, kTileSkinny16 = 4, kTileCols112 = 5
+};
 
 template <bool AK, bool BK_>
 static int launch_layout(int shape, int tile, const DmmaLaunch &L) {
@@ -774,6 +779,7 @@ static int launch_layout(int shape, int tile, const DmmaLaunch &L) {
     return launch_dmma_kernel<AK, BK_, 2, true, Skinny16Cfg>(L);
   if (tile == kTileHalf) return launch_tiles<AK, BK_, 2, HalfCfg>(L);
   if (tile == kTileRows112) return launch_tiles<AK, BK_, 2, Rows112Cfg>(L);
+  if (tile == kTileCols112) return launch_tiles<AK, BK_, 2, Cols112Cfg>(L);
   switch (shape) {
     case 0: return launch_tiles<AK, BK_, 0, MainCfg>(L);
     case 1: return launch_tiles<AK, BK_, 1, MainCfg>(L);
@@ -854,7 +860,15 @@ static GemmPlan choose_plan(int M, int N, int K, int sms, int shape) {
   if (M % MainCfg::BM != 0 && M % Rows112Cfg::BM == 0) {
     GemmPlan p112{kTileRows112, Rows112Cfg::BM, Rows112Cfg::BN,
                   choose_spans(tiles_of(Rows112Cfg::BM, Rows112Cfg::BN), KT, sms)};
-    if (cost(p112, 1.02) < best_cost) best = p112;
+    if (cost(p112, 1.02) < best_cost) {
+      best = p112;
+      best_cost = cost(p112, 1.02);
+    }
+  }
+  if (N % MainCfg::BN != 0 && N % Cols112Cfg::BN == 0) {
+    GemmPlan c112{kTileCols112, Cols112Cfg::BM, Cols112Cfg::BN,
+                  choose_spans(tiles_of(Cols112Cfg::BM, Cols112Cfg::BN), KT, sms)};
+    if (cost(c112, 1.02) < best_cost) best = c112;
   }
   return best;
 }

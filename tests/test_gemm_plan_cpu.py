@@ -36,6 +36,7 @@ def describe(M, N, K, sms=SMS, want_segments=True):
     ((8192, 1024, 1024), (128, 64, False)),     # 512 full tiles would leave the 4th wave half empty
     ((1024, 1024, 8192), (128, 128, True)),
     ((4096, 4096, 4096), (128, 128, False)),
+    ((65536, 784, 1024), (128, 112, False)),    # gradient w.r.t. a 784-wide input: 784 = 7 x 112
 ])
 def test_tile_choice_for_benchmark_shapes(shape, expect):
     bm, bn, spans, items, slots, _ = describe(*shape)

@@ -212,10 +212,11 @@ def _boundary_shapes():
     """Seeded draw of shapes around the tile, k-tile and split boundaries."""
     rng = np.random.default_rng(2024)
     ms = [2, 16, 64, 112, 114, 126, 128, 130, 224, 256, 300, 784, 1000, 2048, 4098]
-    ns = [2, 8, 10, 16, 18, 32, 34, 64, 66, 128, 130, 200, 258, 1024]
-    ks = [2, 10, 16, 18, 32, 100, 512, 1000, 2048, 4098, 9000]
-    out = []
-    for _ in range(40):
+    # (the 112- and 784-wide outputs take the 128 x 112 tile)
+    ns = [2, 8, 10, 16, 18, 32, 34, 64, 66, 112, 128, 130, 200, 258, 784, 1024]
+    ks = [2, 10, 16, 18, 32, 100, 112, 512, 784, 1000, 2048, 4098, 9000]
+    out = [(256, 784, 64), (300, 112, 34), (4098, 784, 1024)]   # 112-column tile with the staged mask
+    for _ in range(48):
         out.append((int(rng.choice(ms)), int(rng.choice(ks)), int(rng.choice(ns))))
     return sorted(set(out))
 
