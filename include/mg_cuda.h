@@ -81,6 +81,14 @@ int mg_download_i32(int *dst_host, const int *src, size_t n);
 int mg_fill(double *dst, double value, size_t n); /* Tensor.cpp:12-13, 73-77; Autograd.cpp:23-25 */
 int mg_copy(double *dst, const double *src, size_t n);
 /* Pinned host staging memory for callers that stream batches in. */
+/* One-element results (no counterpart in the reference: its values are host
+ * memory already).  mg_scalar_mirror enqueues, behind everything on the compute
+ * stream so far, a copy of *src to a pinned slot on a stream of its own and returns
+ * a ticket; mg_scalar_fetch waits for that copy only — not for work enqueued
+ * later — and returns the value.  *expired = 1 (value untouched) when the slot has
+ * been reused by 256 later mirrors: read the value with mg_download then. */
+int mg_scalar_mirror(const double *src, unsigned long long *out_ticket);
+int mg_scalar_fetch(unsigned long long ticket, double *out, int *expired);
 int mg_host_alloc(size_t bytes, void **out_host);
 int mg_host_free(void *host);
 
@@ -192,6 +200,10 @@ int mg_avg_pool_28(const double *x, double *out, size_t batch);
 
 /* ---- optimiser: src/nn.cpp:65-77 ----------------------------------------- */
 int mg_sgd_step(double *param, const double *grad, double lr, size_t n); /* p -= (lr*g) */
+/* The same update for `count` tensors (host arrays of device pointers and sizes)
+ * in one launch per eight tensors; for optimisers over many small parameters. */
+int mg_sgd_step_multi(double *const *params, const double *const *grads, const size_t *sizes, int count,
+                      double lr);
 
 /* ---- events / timing on the compute stream ------------------------------ */
 int mg_event_create(int *out_id);

@@ -51,6 +51,10 @@ public:
   std::vector<double> &host_mutable();
   const std::vector<double> &host_const();
   double peek(size_t index);  // one element, without lending the host view
+  // For a one-element buffer whose producer has just been enqueued: start an
+  // asynchronous copy to the host, so a later read need not wait for kernels
+  // enqueued after the producer.  No effect on larger buffers.
+  void mirror_async();
 
   // Moves the contents into caller-owned device memory (a slice of a flat
   // parameter/gradient buffer) and uses that memory from now on.
@@ -71,6 +75,7 @@ private:
   void settle_upload();  // make the compute stream wait for a pending prefetch
   void sync_device_from_host();
   void sync_host_from_device();
+  bool fetch_mirror(double *value);  // true: *value is the mirrored, still current element
 
   size_t size_ = 0;
   double *dev_ = nullptr;
@@ -81,6 +86,8 @@ private:
   bool host_valid_ = false;  // host_ holds the current values
   unsigned long long write_stamp_ = 0;
   int pending_upload_ = -1;  // event id of a prefetch the compute stream has not waited for
+  unsigned long long mirror_ticket_ = 0;  // pending scalar mirror (0: none)
+  unsigned long long mirror_stamp_ = 0;   // write_stamp_ when the mirror was started
   std::vector<double> host_;
 };
 

@@ -83,6 +83,10 @@ SIGNATURES = {
     "mg_event_wait_bounded": (C.c_int, [C.c_int, C.c_double]),
     "mg_gemm_plan_describe": (C.c_int, [_sz, _sz, _sz, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int),
                                         C.c_int]),
+    "mg_sgd_step_multi": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(_sz), C.c_int,
+                                    C.c_double]),
+    "mg_scalar_mirror": (C.c_int, [C.c_void_p, C.POINTER(C.c_ulonglong)]),
+    "mg_scalar_fetch": (C.c_int, [C.c_ulonglong, C.POINTER(C.c_double), C.POINTER(C.c_int)]),
     "mg_comm_unique_id": (C.c_int, [C.c_char_p]),
     "mg_comm_init": (C.c_int, [C.c_char_p, C.c_int, C.c_int]),
     "mg_comm_destroy": (C.c_int, []),

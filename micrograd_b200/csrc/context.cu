@@ -124,6 +124,8 @@ int mg_init(int device) {
   return init_locked(device);
 }
 
+static void release_mirror_ring_at_shutdown();
+
 int mg_shutdown(void) {
   std::lock_guard<std::mutex> lock(g_init_mutex);
   Context &c = g_ctx;
@@ -132,6 +134,7 @@ int mg_shutdown(void) {
   for (cudaEvent_t ev : g_events)
     if (ev) cudaEventDestroy(ev);
   g_events.clear();
+  release_mirror_ring_at_shutdown();
   if (c.colsum_scratch) cudaFreeAsync(c.colsum_scratch, c.stream);
   if (c.splitk_scratch) cudaFreeAsync(c.splitk_scratch, c.stream);
   cudaStreamSynchronize(c.stream);
@@ -159,11 +162,14 @@ int mg_sm_count(void) {
   return g_ctx.sm_count;
 }
 
+static cudaStream_t g_mirror_stream_for_sync();
+
 int mg_sync(void) {
   MG_ENSURE_INIT();
   MG_CUDA_TRY(cudaStreamSynchronize(g_ctx.stream));
   MG_CUDA_TRY(cudaStreamSynchronize(g_ctx.comm_stream));
   MG_CUDA_TRY(cudaStreamSynchronize(g_ctx.copy_stream));
+  if (g_mirror_stream_for_sync()) MG_CUDA_TRY(cudaStreamSynchronize(g_mirror_stream_for_sync()));
   return MG_OK;
 }
 
@@ -288,6 +294,79 @@ int mg_copy(double *dst, const double *src, size_t n) {
   if (!dst || !src) return fail(MG_ERR_INVALID, "mg_copy: null pointer");
   MG_CUDA_TRY(cudaMemcpyAsync(dst, src, n * sizeof(double), cudaMemcpyDeviceToDevice,
                               g_ctx.stream));
+  return MG_OK;
+}
+
+/* ---- scalar mirrors ---- */
+// A one-element result (a loss, a sum) is usually read by the host a little later,
+// when more work has been enqueued behind it; a plain download would then wait for
+// all of that work.  mg_scalar_mirror copies the value to a pinned slot on a
+// stream of its own right after its producer, and mg_scalar_fetch waits for that
+// copy only.  256 slots, reused in turn; a ticket names slot and generation.
+namespace {
+constexpr int kMirrorSlots = 256;
+struct MirrorRing {
+  double *pinned = nullptr;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr;
+  cudaEvent_t done[kMirrorSlots] = {};
+  unsigned long long generation[kMirrorSlots] = {};
+  unsigned long long issued = 0;
+};
+MirrorRing g_mirror;
+
+int mirror_ring_init() {
+  if (g_mirror.pinned) return MG_OK;
+  MG_CUDA_TRY(cudaMallocHost(&g_mirror.pinned, kMirrorSlots * sizeof(double)));
+  MG_CUDA_TRY(cudaStreamCreateWithFlags(&g_mirror.stream, cudaStreamNonBlocking));
+  MG_CUDA_TRY(cudaEventCreateWithFlags(&g_mirror.fork, cudaEventDisableTiming));
+  for (auto &ev : g_mirror.done) MG_CUDA_TRY(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+  return MG_OK;
+}
+
+void mirror_ring_release() {
+  if (!g_mirror.pinned) return;
+  cudaStreamSynchronize(g_mirror.stream);
+  for (auto &ev : g_mirror.done) cudaEventDestroy(ev);
+  cudaEventDestroy(g_mirror.fork);
+  cudaStreamDestroy(g_mirror.stream);
+  cudaFreeHost(g_mirror.pinned);
+  g_mirror = MirrorRing();
+}
+}  // namespace
+
+static void release_mirror_ring_at_shutdown() { mirror_ring_release(); }
+static cudaStream_t g_mirror_stream_for_sync() { return g_mirror.stream; }
+
+int mg_scalar_mirror(const double *src, unsigned long long *out_ticket) {
+  MG_ENSURE_INIT();
+  if (!src || !out_ticket) return fail(MG_ERR_INVALID, "mg_scalar_mirror: null pointer");
+  int rc = mirror_ring_init();
+  if (rc != MG_OK) return rc;
+  MirrorRing &m = g_mirror;
+  const unsigned long long ticket = ++m.issued;
+  const int slot = (int)(ticket % kMirrorSlots);
+  m.generation[slot] = ticket;
+  MG_CUDA_TRY(cudaEventRecord(m.fork, g_ctx.stream));
+  MG_CUDA_TRY(cudaStreamWaitEvent(m.stream, m.fork, 0));
+  MG_CUDA_TRY(cudaMemcpyAsync(m.pinned + slot, src, sizeof(double), cudaMemcpyDeviceToHost, m.stream));
+  MG_CUDA_TRY(cudaEventRecord(m.done[slot], m.stream));
+  *out_ticket = ticket;
+  return MG_OK;
+}
+
+int mg_scalar_fetch(unsigned long long ticket, double *out, int *expired) {
+  MG_ENSURE_INIT();
+  if (!out || !expired) return fail(MG_ERR_INVALID, "mg_scalar_fetch: null pointer");
+  MirrorRing &m = g_mirror;
+  const int slot = (int)(ticket % kMirrorSlots);
+  if (!m.pinned || ticket == 0 || m.generation[slot] != ticket) {
+    *expired = 1;  // the slot has been reused since: read the value the ordinary way
+    return MG_OK;
+  }
+  MG_CUDA_TRY(cudaEventSynchronize(m.done[slot]));
+  *out = m.pinned[slot];
+  *expired = 0;
   return MG_OK;
 }
 

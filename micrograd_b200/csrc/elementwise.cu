@@ -446,6 +446,39 @@ static int binary_bwd_one(const double *a, const double *b, const double *g, dou
   return launch_map(f, n, "binary_bwd");
 }
 
+// Several small parameter tensors in one launch (the per-tensor form costs a
+// launch each, which is all a batch-1 training step consists of).  p - (lr*g)
+// with the product rounded first, like SgdFn.
+struct SgdBatch {
+  double *param[8];
+  const double *grad[8];
+  unsigned long long n[8];
+  int count;
+};
+
+__global__ void __launch_bounds__(256) sgd_multi_kernel(SgdBatch b, double lr) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (int t = 0; t < b.count; t++) {
+    double *p = b.param[t];
+    const double *g = b.grad[t];
+    const size_t n = (size_t)b.n[t];
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g)) & 15) == 0) {
+      const size_t pairs = n >> 1;
+      for (; i < pairs; i += stride) {
+        double2 pv = reinterpret_cast<double2 *>(p)[i];
+        const double2 gv = reinterpret_cast<const double2 *>(g)[i];
+        pv.x = pv.x - lr * gv.x;
+        pv.y = pv.y - lr * gv.y;
+        reinterpret_cast<double2 *>(p)[i] = pv;
+      }
+      if ((n & 1) && blockIdx.x == 0 && threadIdx.x == 0) p[n - 1] = p[n - 1] - lr * g[n - 1];
+    } else {
+      for (; i < n; i += stride) p[i] = p[i] - lr * g[i];
+    }
+  }
+}
+
 extern "C" {
 
 int mg_fill(double *dst, double value, size_t n) {
@@ -539,6 +572,32 @@ int mg_sgd_step(double *param, const double *grad, double lr, size_t n) {
   SgdFn f;
   f.in[0] = param; f.in[1] = grad; f.out[0] = param; f.lr = lr;
   return launch_map(f, n, "sgd_step");
+}
+
+int mg_sgd_step_multi(double *const *params, const double *const *grads, const size_t *sizes, int count,
+                      double lr) {
+  MG_ENSURE_INIT();
+  if (count <= 0) return MG_OK;
+  if (!params || !grads || !sizes) return fail(MG_ERR_INVALID, "mg_sgd_step_multi: null pointer");
+  Context &c = ctx();
+  for (int first = 0; first < count; first += 8) {
+    SgdBatch b;
+    b.count = 0;
+    size_t longest = 0;
+    for (int t = first; t < count && t < first + 8; t++) {
+      if (sizes[t] == 0) continue;
+      if (!params[t] || !grads[t]) return fail(MG_ERR_INVALID, "mg_sgd_step_multi: null tensor %d", t);
+      b.param[b.count] = params[t];
+      b.grad[b.count] = grads[t];
+      b.n[b.count] = sizes[t];
+      longest = sizes[t] > longest ? sizes[t] : longest;
+      b.count++;
+    }
+    if (b.count == 0) continue;
+    sgd_multi_kernel<<<grid_for(longest, 256, 8), 256, 0, c.stream>>>(b, lr);
+    MG_LAUNCH_CHECK("sgd_multi");
+  }
+  return MG_OK;
 }
 
 int mg_add_row_fwd(const double *x, const double *row, double *out, size_t M, size_t N) {

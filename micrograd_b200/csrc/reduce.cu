@@ -383,6 +383,13 @@ int mg_add_row_bwd(const double *g, double *gx, double *grow, size_t M, size_t N
     // Only the pass-through: a plain accumulate.
     return mg_unary_bwd(MG_SADD, nullptr, nullptr, 0.0, g, gx, M * N, flags & MG_ACC_STORE_A);
   }
+  if (M == 1) {
+    // A single row is its own column sum: one accumulate per destination instead
+    // of the two-stage reduction (batch-1 training steps are all launch cost).
+    int rc = mg_unary_bwd(MG_SADD, nullptr, nullptr, 0.0, g, grow, N, (flags & MG_ACC_STORE_B) ? MG_ACC_STORE_A : 0);
+    if (rc != MG_OK || !gx) return rc;
+    return mg_unary_bwd(MG_SADD, nullptr, nullptr, 0.0, g, gx, N, flags & MG_ACC_STORE_A);
+  }
   Context &c = ctx();
   uintptr_t bits = reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(gx);
   const bool vec = (N % 2 == 0) && (bits & 15) == 0;

@@ -86,8 +86,33 @@ void Storage::sync_device_from_host() {
 
 void Storage::sync_host_from_device() {
   host_.resize(size_);
-  check(mg_download(host_.data(), dev_, size_), "download");
+  double mirrored = 0.0;
+  if (fetch_mirror(&mirrored)) {
+    host_[0] = mirrored;
+  } else {
+    check(mg_download(host_.data(), dev_, size_), "download");
+  }
   host_valid_ = true;
+}
+
+// A one-element result is copied to pinned host memory right behind its producer,
+// so that a host read some kernels later waits for that copy and not for the
+// whole queue (a training loop reads its loss after enqueueing the backward pass).
+void Storage::mirror_async() {
+  if (size_ != 1 || zero_ || !dev_valid_ || !dev_) {
+    return;
+  }
+  check(mg_scalar_mirror(dev_, &mirror_ticket_), "scalar mirror");
+  mirror_stamp_ = write_stamp_;
+}
+
+bool Storage::fetch_mirror(double *value) {
+  if (mirror_ticket_ == 0 || mirror_stamp_ != write_stamp_ || size_ != 1) {
+    return false;  // no mirror, or the contents were rewritten since
+  }
+  int expired = 0;
+  check(mg_scalar_fetch(mirror_ticket_, value, &expired), "scalar fetch");
+  return expired == 0;
 }
 
 const double *Storage::device_read() {
@@ -159,8 +184,8 @@ void Storage::fill(double value) {
 }
 
 std::vector<double> &Storage::host_mutable() {
+  host_const();  // (before the stamp moves: a pending scalar mirror is still current here)
   write_stamp_++;
-  host_const();
   // The caller may write through the reference at any later time, so the host
   // vector is the authority until a kernel needs the values again.
   dev_valid_ = false;
@@ -189,6 +214,9 @@ double Storage::peek(size_t index) {
     return host_[index];
   }
   double v = 0.0;
+  if (fetch_mirror(&v)) {
+    return v;
+  }
   check(mg_download(&v, dev_ + index, 1), "download");
   return v;
 }

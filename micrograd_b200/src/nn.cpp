@@ -183,14 +183,21 @@ void SGD::step() {
     }
     check(mg_sgd_step(flat_data_, flat_grad_, learning_rate_, flat_elems_), "sgd step");
   } else {
+    // One launch per eight parameter tensors.
+    std::vector<double *> params;
+    std::vector<const double *> grads;
+    std::vector<size_t> sizes;
     for (auto &p : parameters_) {
       if (Access::grad(*p).is_zero()) {
         continue;
       }
-      check(mg_sgd_step(Access::data(*p).device_update(), Access::grad(*p).device_read(),
-                        learning_rate_, p->size()),
-            "sgd step");
+      params.push_back(Access::data(*p).device_update());
+      grads.push_back(Access::grad(*p).device_read());
+      sizes.push_back(p->size());
     }
+    check(mg_sgd_step_multi(params.data(), grads.data(), sizes.data(), static_cast<int>(params.size()),
+                            learning_rate_),
+          "sgd step");
   }
   std::fill(ready_.begin(), ready_.end(), 0);
 }
@@ -310,6 +317,7 @@ static std::shared_ptr<Tensor> xent_node(const std::shared_ptr<Tensor> &logits,
   check(mg_softmax_xent_fwd(Access::data(*logits).device_read(), ids->get(),
                             Access::data(*result).device_overwrite(), rows, classes, denom),
         "softmax cross-entropy");
+  Access::data(*result).mirror_async();
   Access::backward_fn(*result) = [ids, rows, classes, denom](Tensor &self) {
     Tensor &z = *Access::children(self)[0];
     if (Access::grad(self).is_zero() || !Access::requires_grad(z)) {

@@ -19,6 +19,7 @@ std::shared_ptr<Tensor> Tensor::binary_op(int op, const char *label,
   check(mg_binary_fwd(op, data_.device_read(), b->data_.device_read(),
                       result->data_.device_overwrite(), size()),
         label);
+  result->data_.mirror_async();  // one-element results only
 
   result->backward_fn_ = [op](Tensor &self) {
     if (self.grad_.is_zero()) {
@@ -106,6 +107,7 @@ std::shared_ptr<Tensor> Tensor::unary_op(int op, std::string label, double scala
   auto result = make_result(shape_, std::move(label), {shared_from_this()});
   check(mg_unary_fwd(op, data_.device_read(), scalar, result->data_.device_overwrite(), size()),
         "unary forward");
+  result->data_.mirror_async();  // one-element results only (e.g. the mean of mse_loss)
   result->backward_fn_ = [op, scalar](Tensor &self) {
     Tensor &x = *self.children_[0];
     if (self.grad_.is_zero() || !x.requires_grad_) {

@@ -10,6 +10,7 @@ using micrograd::detail::check;
 std::shared_ptr<Tensor> Tensor::sum() {
   auto result = make_result({1}, "sum", {shared_from_this()});
   check(mg_sum_all_fwd(data_.device_read(), result->data_.device_overwrite(), size()), "sum");
+  result->data_.mirror_async();
 
   // The upstream scalar is read on the device; it never visits the host.
   result->backward_fn_ = [](Tensor &self) {

@@ -192,6 +192,57 @@ def test_sgd_step_and_fill_bit_exact(abi, fast, n):
     assert not dp.numpy().any()
 
 
+@pytest.mark.parametrize("sizes", [[1], [19600, 100, 1000, 10], [7, 0, 4097, 33, 2, 100352, 128, 8192, 64, 640, 10],
+                                   [1863690]])
+def test_multi_tensor_sgd_step_bit_exact(abi, fast, sizes):
+    """One launch per eight parameter tensors; p - (lr*g) with the product rounded
+    first, bit for bit like the per-tensor form (slices at odd 8-byte offsets and
+    empty tensors included)."""
+    import ctypes as C
+    rng = np.random.default_rng(len(sizes) * 100 + sizes[0])
+    total = sum(sizes) + len(sizes)
+    p, g = rng.standard_normal(total), rng.standard_normal(total)
+    dp, dg = abi.array(p), abi.array(g)
+    offs, o = [], 0
+    for i, n in enumerate(sizes):
+        offs.append(o)
+        o += n + (i % 2)                      # every other tensor starts 8 bytes off a 16-byte boundary
+    P = (C.c_void_p * len(sizes))(*[dp.offset(a) for a in offs])
+    G = (C.c_void_p * len(sizes))(*[dg.offset(a) for a in offs])
+    S = (C.c_size_t * len(sizes))(*sizes)
+    abi.mg_sgd_step_multi(P, G, S, len(sizes), 0.01)
+    ref = p.copy()
+    for a, n in zip(offs, sizes):
+        fast.sgd_step(ref[a:a + n], g[a:a + n], 0.01)
+    assert np.array_equal(dp.numpy(), ref)
+
+
+def test_scalar_mirror_returns_the_value_at_enqueue_time(abi):
+    """A mirrored scalar is read back without waiting for later work, keeps the
+    value it had when the mirror was enqueued, and its ticket expires once the
+    256-slot ring has gone round."""
+    import ctypes as C
+    x = abi.array(np.array([3.25]))
+    t = C.c_ulonglong()
+    abi.mg_scalar_mirror(x.ptr, C.byref(t))
+    abi.mg_fill(x.ptr, 7.0, 1)                              # later write: not seen by the mirror
+    big = abi.empty(1 << 24)
+    abi.mg_fill(big.ptr, 1.0, 1 << 24)                      # later work the fetch does not wait for
+    v, expired = C.c_double(), C.c_int()
+    abi.mg_scalar_fetch(t.value, C.byref(v), C.byref(expired))
+    assert expired.value == 0 and v.value == 3.25
+    assert x.numpy()[0] == 7.0
+    first = t.value
+    for i in range(256):
+        abi.mg_scalar_mirror(x.ptr, C.byref(t))
+    abi.mg_scalar_fetch(first, C.byref(v), C.byref(expired))
+    assert expired.value == 1
+    abi.mg_scalar_fetch(t.value, C.byref(v), C.byref(expired))
+    assert expired.value == 0 and v.value == 7.0
+    abi.mg_scalar_fetch(0, C.byref(v), C.byref(expired))
+    assert expired.value == 1
+
+
 @pytest.mark.parametrize("M,N", [(1, 1), (3, 5), (32, 10), (257, 128), (1024, 1024), (4099, 33)])
 def test_add_row_forward(abi, fast, M, N):
     rng = np.random.default_rng(M * 131 + N)

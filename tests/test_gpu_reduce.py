@@ -81,7 +81,8 @@ def test_sum_lastaxis(abi, fast, M, N):
     assert np.array_equal(dgx.numpy((M, N)), np.repeat(g[:, None], N, axis=1))
 
 
-@pytest.mark.parametrize("M,N", [(1, 1), (3, 5), (32, 10), (257, 128), (1000, 33), (4096, 1024), (65536, 10)])
+@pytest.mark.parametrize("M,N", [(1, 1), (1, 11), (1, 100), (3, 5), (32, 10), (257, 128), (1000, 33),
+                                 (4096, 1024), (65536, 10)])
 def test_add_row_backward(abi, fast, M, N):
     rng = np.random.default_rng(M + 17 * N)
     g = rng.standard_normal((M, N))
