@@ -15,7 +15,9 @@
  *   - Work is enqueued on one ordered compute stream per process and returns
  *     without waiting; only mg_download*, mg_sync, mg_event_elapsed_ms and the
  *     bounded waits block the host.
- *   - One device per process (one process per GPU).  mg_init() is implicit: the
+ *   - One device per process (one process per GPU), and calls are expected from
+ *     threads that have that device current (the thread that ran mg_init does;
+ *     any other thread calls cudaSetDevice(mg_device()) first).  mg_init() is implicit: the
  *     first call that needs the device initialises it from MG_DEVICE, else
  *     LOCAL_RANK, else device 0.  There is no CPU fallback: without a usable
  *     CUDA device every call fails with MG_ERR_CUDA.
@@ -55,6 +57,14 @@ int mg_device(void); /* current device ordinal, -1 before init */
 int mg_sm_count(void);
 int mg_sync(void);                 /* wait for the compute and comm streams */
 int mg_check_kernel_status(void);  /* MG_ERR_KERNEL if a kernel raised its fault flag (syncs) */
+/* The same fault word without a device synchronisation: mg_kernel_status_mirror()
+ * enqueues, behind everything on the compute stream so far, a copy of the word to
+ * pinned host memory; mg_kernel_status_peek() returns the value the most recent
+ * completed copy delivered (0 before the first).  A training loop mirrors once per
+ * step behind its gradient exchange and peeks at the start of the next step, so a
+ * timed-out exchange is seen one step later without ever stalling the device. */
+int mg_kernel_status_mirror(void);
+int mg_kernel_status_peek(int *out_status);
 int mg_mem_info(size_t *free_bytes, size_t *total_bytes);
 
 /* ---- storage ----------------------------------------------------------- */
@@ -78,6 +88,11 @@ int mg_upload_async(double *dst, const double *src_host, size_t n, int *out_even
 int mg_compute_wait_event(int id); /* compute stream waits for the event, not the host */
 int mg_upload_i32(int *dst, const int *src_host, size_t n);
 int mg_download_i32(int *dst_host, const int *src, size_t n);
+/* Byte data (image pixels) from host memory: dst[i] = (double)src_host[i] / divisor,
+ * the division done on the device after an upload of n bytes instead of 8n — the
+ * `pixel / 255.0` of src/mnist.cpp:21, exactly rounded like the host's.  src_host
+ * may be released once the call returns only if it is pageable memory. */
+int mg_upload_u8_scaled(double *dst, const unsigned char *src_host, size_t n, double divisor);
 int mg_fill(double *dst, double value, size_t n); /* Tensor.cpp:12-13, 73-77; Autograd.cpp:23-25 */
 int mg_copy(double *dst, const double *src, size_t n);
 /* Pinned host staging memory for callers that stream batches in. */
@@ -129,8 +144,11 @@ int mg_add_row_bwd(const double *g, double *gx, double *grow, size_t M, size_t N
  * library holds it until the process exits).
  *   - mg_init() must have run earlier, at set-up time (it allocates); this entry
  *     point never initialises implicitly and fails with MG_ERR_INVALID otherwise.
- *   - The first call on a device looks up the array's device address; make that
- *     first call before starting any stream capture.
+ *   - The first call looks up the array's address on the device the library is
+ *     bound to; make that first call before starting any stream capture.  The
+ *     calling thread must have that device current (a new host thread starts on
+ *     device 0): otherwise the call fails with MG_ERR_INVALID instead of creating
+ *     a context on another GPU.
  *   - Limit: N <= 131072 columns (any M); more is rejected with MG_ERR_INVALID and
  *     a message naming the pooled alternative, mg_add_row_bwd(g, NULL, out_row, ..).
  *   - All calls share the one array.  Each call overwrites every partial it later

@@ -81,6 +81,11 @@ public:
   // Uploads straight from caller memory (pinned or pageable) without the
   // intermediate std::vector the reference constructor takes by value.
   static std::shared_ptr<Tensor> from_host(std::vector<size_t> shape, const double *values);
+  // Read-only host views.  Unlike the mutable data()/grad() of the reference
+  // interface they do not hand out a writable reference, so the device copy stays
+  // current and no re-upload follows the read.
+  const std::vector<double> &data() const;
+  const std::vector<double> &grad() const;
 
 private:
   // Shared bodies of the public ops (op codes are those of mg_cuda.h).

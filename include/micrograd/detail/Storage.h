@@ -69,10 +69,14 @@ public:
   // Counts every hand-out of the contents for writing (device or host); lets a
   // caller detect that nobody has touched the buffer since it last looked.
   unsigned long long write_stamp() const { return write_stamp_; }
+  // Marks the buffer as the target of an all-reduce still running on the
+  // communication stream; the next host read joins that stream first.
+  void set_exchange_pending(bool pending) { comm_pending_ = pending; }
 
 private:
   void ensure_device_buffer();
   void settle_upload();  // make the compute stream wait for a pending prefetch
+  void settle_exchange();  // make the compute stream wait for a pending all-reduce
   void sync_device_from_host();
   void sync_host_from_device();
   bool fetch_mirror(double *value);  // true: *value is the mirrored, still current element
@@ -85,6 +89,7 @@ private:
   bool dev_valid_ = false;   // dev_ holds the current values
   bool host_valid_ = false;  // host_ holds the current values
   unsigned long long write_stamp_ = 0;
+  bool comm_pending_ = false;  // an all-reduce on the communication stream targets dev_
   int pending_upload_ = -1;  // event id of a prefetch the compute stream has not waited for
   unsigned long long mirror_ticket_ = 0;  // pending scalar mirror (0: none)
   unsigned long long mirror_stamp_ = 0;   // write_stamp_ when the mirror was started

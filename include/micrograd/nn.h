@@ -8,6 +8,7 @@
 #include <vector>
 
 #include "Tensor.h"
+#include "detail/GradBuckets.h"
 
 std::shared_ptr<Tensor> mse_loss(const std::shared_ptr<Tensor> &prediction,
                                  const std::shared_ptr<Tensor> &target);
@@ -46,6 +47,11 @@ public:
   // buffers and, when a communicator is up (micrograd::comm_init), sums each
   // parameter's gradient across ranks as soon as backward() has finished it.
   // step() then waits for those sums on the device, not on the host.
+  // Parameters travel in one message per layer: a weight directly followed by
+  // its bias forms a pair, anything else goes alone.  A parameter that the
+  // backward sweep never reaches is reduced by step() itself, and a second
+  // backward() before step() throws std::logic_error once sums have been
+  // exchanged (they cannot be accumulated into).
   void enable_allreduce();
 
 private:
@@ -56,7 +62,9 @@ private:
   double *flat_data_ = nullptr;
   double *flat_grad_ = nullptr;
   std::vector<size_t> offsets_;
-  std::vector<char> ready_;
+  micrograd::detail::GradBuckets buckets_;
+  void reduce_bucket(size_t bucket);
+  std::vector<char> requires_flags() const;
   size_t flat_elems_ = 0;
   bool allreduce_ = false;
 };

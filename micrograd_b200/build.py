@@ -120,50 +120,55 @@ def reference_dir() -> str:
 
 
 def build_cpp_tests(force: bool = False, verbose: bool = False, reference: str | None = None):
-    """C++ test binaries (run by tests/test_gpu_cpp.py on a GPU machine):
+    """C++ test binaries, all under tests/cpp/bin/:
 
-    tests/cpp/bin/api_test         this repository's own C++ API tests
-    oracle/_ref/tensor_test_b200   the reference's test/tensor_test.cpp, compiled
-                                   unchanged against this backend's headers and
-                                   library — only where the reference tree is
-                                   mounted; elsewhere the prebuilt binary is used.
+    buckets_test       CPU-only unit tests of the data-parallel bookkeeping
+                       (header-only logic, no CUDA link; run by the CPU test suite)
+    api_test           this repository's own C++ API tests (GPU)
+    trainer_loop       the reference trainer's per-sample loop on synthetic images (GPU)
+    tensor_test_b200   the reference's test/tensor_test.cpp, compiled unchanged
+                       against this backend's headers and library — only where
+                       the reference tree is mounted; elsewhere the prebuilt
+                       binary is used.
+    main_b200          the reference's src/main.cpp, compiled unchanged.
     """
     tests = os.path.join(ROOT, "tests", "cpp")
     bindir = os.path.join(tests, "bin")
     os.makedirs(bindir, exist_ok=True)
     common = [CXX, "-O2", "-std=c++20", f"-I{INCLUDE}", f"-I{tests}"]
     link = [f"-L{LIB}", "-lmicrograd", "-lmg_cuda"]
+    rpath = ["-Wl,-rpath,$ORIGIN/../../../micrograd_b200/lib"]
     lib = os.path.join(LIB, "libmicrograd.so")
+    gtest = os.path.join(tests, "gtest", "gtest.h")
     built = []
+    out = os.path.join(bindir, "buckets_test")
+    src = os.path.join(tests, "buckets_test.cpp")
+    if force or _newer(out, [src, gtest, os.path.join(INCLUDE, "micrograd", "detail", "GradBuckets.h")]):
+        _run(common + [src, "-o", out], verbose)
+    built.append(out)
     out = os.path.join(bindir, "api_test")
     src = os.path.join(tests, "api_test.cpp")
-    if force or _newer(out, [src, lib, os.path.join(tests, "gtest", "gtest.h")]):
-        _run(common + [src, "-o", out] + link + ["-Wl,-rpath,$ORIGIN/../../../micrograd_b200/lib"],
-             verbose)
+    if force or _newer(out, [src, lib, gtest]):
+        _run(common + [src, "-o", out] + link + rpath, verbose)
     built.append(out)
     out = os.path.join(bindir, "trainer_loop")
     src = os.path.join(tests, "trainer_loop.cpp")
     if force or _newer(out, [src, lib]):
-        _run(common + [src, "-o", out] + link + ["-Wl,-rpath,$ORIGIN/../../../micrograd_b200/lib"],
-             verbose)
+        _run(common + [src, "-o", out] + link + rpath, verbose)
     built.append(out)
     reference = reference or reference_dir()
     ref_test = os.path.join(reference, "test", "tensor_test.cpp")
     if os.path.exists(ref_test):
-        refdir = os.path.join(ROOT, "oracle", "_ref")
-        os.makedirs(refdir, exist_ok=True)
-        out = os.path.join(refdir, "tensor_test_b200")
+        out = os.path.join(bindir, "tensor_test_b200")
         if force or _newer(out, [ref_test, lib]):
-            _run(common + [ref_test, "-o", out] + link +
-                 ["-Wl,-rpath,$ORIGIN/../../micrograd_b200/lib"], verbose)
+            _run(common + [ref_test, "-o", out] + link + rpath, verbose)
         built.append(out)
         # the reference's trainer application, compiled unchanged (it needs MNIST
         # files under ./data to do anything; building it proves the API surface)
         ref_main = os.path.join(reference, "src", "main.cpp")
-        out = os.path.join(refdir, "main_b200")
+        out = os.path.join(bindir, "main_b200")
         if os.path.exists(ref_main) and (force or _newer(out, [ref_main, lib])):
-            _run([CXX, "-O2", "-std=c++20", f"-I{INCLUDE}", ref_main, "-o", out] + link +
-                 ["-Wl,-rpath,$ORIGIN/../../micrograd_b200/lib"], verbose)
+            _run([CXX, "-O2", "-std=c++20", f"-I{INCLUDE}", ref_main, "-o", out] + link + rpath, verbose)
         built.append(out)
     return built
 

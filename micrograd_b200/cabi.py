@@ -35,6 +35,8 @@ SIGNATURES = {
     "mg_sm_count": (C.c_int, []),
     "mg_sync": (C.c_int, []),
     "mg_check_kernel_status": (C.c_int, []),
+    "mg_kernel_status_mirror": (C.c_int, []),
+    "mg_kernel_status_peek": (C.c_int, [_ip]),
     "mg_mem_info": (C.c_int, [C.POINTER(_sz), C.POINTER(_sz)]),
     "mg_alloc": (C.c_int, [_sz, C.POINTER(C.c_void_p)]),
     "mg_free": (C.c_int, [C.c_void_p]),
@@ -46,6 +48,7 @@ SIGNATURES = {
     "mg_compute_wait_event": (C.c_int, [C.c_int]),
     "mg_upload_i32": (C.c_int, [C.c_void_p, C.c_void_p, _sz]),
     "mg_download_i32": (C.c_int, [C.c_void_p, C.c_void_p, _sz]),
+    "mg_upload_u8_scaled": (C.c_int, [C.c_void_p, C.c_void_p, _sz, C.c_double]),
     "mg_fill": (C.c_int, [C.c_void_p, C.c_double, _sz]),
     "mg_copy": (C.c_int, [C.c_void_p, C.c_void_p, _sz]),
     "mg_host_alloc": (C.c_int, [_sz, C.POINTER(C.c_void_p)]),

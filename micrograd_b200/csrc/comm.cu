@@ -50,7 +50,12 @@ long long peer_wait_cycles() {
   static const long long v = [] {
     const char *e = std::getenv("MG_PEER_WAIT_MS");
     const long long ms = e && *e ? std::atoll(e) : 10000;
-    return (ms < 1 ? 1 : ms) * 1965000ll;
+    // clock64() ticks at the SM clock; take the device's maximum (in kHz = cycles
+    // per millisecond), so the limit is at least the requested time.
+    int khz = 0;
+    if (cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ctx().device) != cudaSuccess || khz <= 0)
+      khz = 2000000;
+    return (ms < 1 ? 1 : ms) * (long long)khz;
   }();
   return v;
 }
@@ -236,7 +241,8 @@ int peer_ctas() {
   static const int v = [] {
     const char *e = std::getenv("MG_PEER_CTAS");
     int n = e && *e ? std::atoi(e) : 16;
-    return n < 1 ? 1 : (n > 148 ? 148 : n);
+    const int sms = ctx().sm_count > 0 ? ctx().sm_count : 1;
+    return n < 1 ? 1 : (n > sms ? sms : n);
   }();
   return v;
 }

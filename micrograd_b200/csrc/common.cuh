@@ -39,6 +39,7 @@ struct Context {
   size_t splitk_scratch_elems = 0;
   // Kernel fault word: kernels write a non-zero code here instead of trapping.
   int *kernel_status = nullptr;        // device
+  int *status_host = nullptr;          // pinned mirror of kernel_status (mg_kernel_status_mirror)
   // L2 flush buffer.
   void *flush_buf = nullptr;
   size_t flush_bytes = 0;

@@ -142,6 +142,7 @@ int mg_shutdown(void) {
   cudaFree(c.reduce_partials);
   cudaFree(c.reduce_ticket);
   cudaFree(c.kernel_status);
+  if (c.status_host) cudaFreeHost(c.status_host);
   if (c.flush_buf) cudaFree(c.flush_buf);
   cudaEventDestroy(c.copy_fork_event);
   cudaStreamDestroy(c.copy_stream);
@@ -181,9 +182,29 @@ int mg_check_kernel_status(void) {
   MG_CUDA_TRY(cudaStreamSynchronize(g_ctx.stream));
   if (status != 0) {
     cudaMemsetAsync(g_ctx.kernel_status, 0, sizeof(int), g_ctx.stream);
+    if (g_ctx.status_host) *g_ctx.status_host = 0;
     return fail(MG_ERR_KERNEL, "a kernel raised fault code %d (bounded wait expired or bad geometry)",
                 status);
   }
+  return MG_OK;
+}
+
+int mg_kernel_status_mirror(void) {
+  MG_ENSURE_INIT();
+  Context &c = g_ctx;
+  if (!c.status_host) {
+    MG_CUDA_TRY(cudaMallocHost(&c.status_host, sizeof(int)));
+    *c.status_host = 0;
+  }
+  MG_CUDA_TRY(cudaMemcpyAsync(c.status_host, c.kernel_status, sizeof(int), cudaMemcpyDeviceToHost,
+                              c.stream));
+  return MG_OK;
+}
+
+int mg_kernel_status_peek(int *out_status) {
+  if (!out_status) return fail(MG_ERR_INVALID, "mg_kernel_status_peek: null pointer");
+  const volatile int *host = g_ctx.status_host;
+  *out_status = host ? *host : 0;
   return MG_OK;
 }
 

@@ -397,6 +397,15 @@ __global__ void avg_pool_28_kernel(const double *__restrict__ x, double *__restr
   }
 }
 
+// dst[i] = src[i] / divisor, the byte widened to double first (pixel / 255.0 of
+// src/mnist.cpp:21: one IEEE division, so the values equal the host's).
+__global__ void u8_scale_kernel(const unsigned char *__restrict__ src, double *__restrict__ dst,
+                                size_t n, double divisor) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    dst[i] = (double)src[i] / divisor;
+}
+
 __global__ void f64_to_i32_kernel(const double *__restrict__ src, int *__restrict__ dst, size_t n) {
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
@@ -652,6 +661,21 @@ int mg_avg_pool_28(const double *x, double *out, size_t batch) {
   if (!x || !out) return fail(MG_ERR_INVALID, "mg_avg_pool_28: null pointer");
   avg_pool_28_kernel<<<grid_for(batch * 196, 256, 8), 256, 0, ctx().stream>>>(x, out, batch);
   MG_LAUNCH_CHECK("avg_pool_28");
+  return MG_OK;
+}
+
+int mg_upload_u8_scaled(double *dst, const unsigned char *src_host, size_t n, double divisor) {
+  MG_ENSURE_INIT();
+  if (n == 0) return MG_OK;
+  if (!dst || !src_host) return fail(MG_ERR_INVALID, "mg_upload_u8_scaled: null pointer");
+  if (divisor == 0.0) return fail(MG_ERR_INVALID, "mg_upload_u8_scaled: divisor is zero");
+  Context &c = ctx();
+  unsigned char *staged = nullptr;
+  MG_CUDA_TRY(cudaMallocAsync(&staged, n, c.stream));
+  MG_CUDA_TRY(cudaMemcpyAsync(staged, src_host, n, cudaMemcpyHostToDevice, c.stream));
+  u8_scale_kernel<<<grid_for(n, 256, 8), 256, 0, c.stream>>>(staged, dst, n, divisor);
+  MG_LAUNCH_CHECK("u8_scale");
+  MG_CUDA_TRY(cudaFreeAsync(staged, c.stream));
   return MG_OK;
 }
 

@@ -8,6 +8,8 @@
 // size, never on scheduling, so a result is reproducible from run to run.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace mg {
 
 __device__ __forceinline__ double warp_sum(double v) {
@@ -398,7 +400,7 @@ int mg_add_row_bwd(const double *g, double *gx, double *grow, size_t M, size_t N
   const int TY = 256 / TX;
   const size_t gridx = (ncol + TX - 1) / TX;
   // Row chunks: about four waves of CTAs, each CTA at least 4 passes of TY rows.
-  size_t S = (size_t)(148 * 4) / gridx;
+  size_t S = (size_t)(c.sm_count * 4) / gridx;
   size_t max_s = (M + (size_t)TY * 4 - 1) / ((size_t)TY * 4);
   if (S > max_s) S = max_s;
   if (S < 1) S = 1;
@@ -494,12 +496,25 @@ constexpr int kNoAllocMaxDevices = 64;
 static __device__ __align__(256) double g_noalloc_colsum_scratch[kNoAllocScratchElems];
 static double *g_noalloc_scratch_addr[kNoAllocMaxDevices];  // per device, filled on first use
 
-// Device address of the static scratch on the current device (looked up once).
+// Device address of the static scratch on the context's device (looked up once,
+// under a lock).  The lookup is keyed on the device the context is bound to, and
+// refused when the calling thread has a different device current: a fresh host
+// thread starts on device 0, and resolving the symbol there would create a
+// context (an allocation) on a GPU this process does not use.
+static std::mutex g_noalloc_mutex;
+
 static int noalloc_scratch(double **out) {
-  int device = -1;
-  MG_CUDA_TRY(cudaGetDevice(&device));
+  const int device = ctx().device;
+  int current = -1;
+  MG_CUDA_TRY(cudaGetDevice(&current));
+  if (current != device)
+    return fail(MG_ERR_INVALID,
+                "mg_colsum_noalloc: the calling thread has device %d current but the library is "
+                "bound to device %d; call cudaSetDevice(%d) on this thread first",
+                current, device, device);
   if (device < 0 || device >= kNoAllocMaxDevices)
     return fail(MG_ERR_INVALID, "mg_colsum_noalloc: device ordinal %d not supported", device);
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
   if (!g_noalloc_scratch_addr[device]) {
     double *ptr = nullptr;
     cudaError_t e = cudaGetSymbolAddress((void **)&ptr, g_noalloc_colsum_scratch);
@@ -537,7 +552,7 @@ extern "C" int mg_colsum_noalloc(const double *g, double *out_row, size_t M, siz
   const int TY = 256 / TX;
   const size_t gridx = (ncol + TX - 1) / TX;
   // Row chunks as in the pooled path, capped so that S x N partials fit the array.
-  size_t S = (size_t)(148 * 4) / gridx;
+  size_t S = (size_t)(c.sm_count * 4) / gridx;
   const size_t max_rows = (M + (size_t)TY * 4 - 1) / ((size_t)TY * 4);
   const size_t max_fit = kNoAllocScratchElems / N;
   if (S > max_rows) S = max_rows;

@@ -14,6 +14,7 @@
 #include <memory>
 #include <stdexcept>
 #include <string>
+#include <utility>
 #include <vector>
 
 struct mgt_tensor_s {
@@ -118,9 +119,18 @@ void mgt_shape(mgt_tensor t, size_t *out) {
 
 size_t mgt_size(mgt_tensor t) { return t->p->size(); }
 
+// With the B200 backend the getters read through the const accessors: a mutable
+// data()/grad() reference would mark the device copy stale and force a re-upload
+// before the next kernel.  The reference has only the mutable accessors.
+#ifdef MG_B200_EXTENSIONS
+#define MGT_READ_VIEW(tensor) std::as_const(*(tensor))
+#else
+#define MGT_READ_VIEW(tensor) (*(tensor))
+#endif
+
 int mgt_get_data(mgt_tensor t, double *out, size_t n) {
   return guard_int([&] {
-    auto &v = t->p->data();
+    auto &v = MGT_READ_VIEW(t->p).data();
     if (n != v.size()) {
       throw std::invalid_argument("mgt_get_data: size mismatch");
     }
@@ -130,7 +140,7 @@ int mgt_get_data(mgt_tensor t, double *out, size_t n) {
 
 int mgt_get_grad(mgt_tensor t, double *out, size_t n) {
   return guard_int([&] {
-    auto &v = t->p->grad();
+    auto &v = MGT_READ_VIEW(t->p).grad();
     if (n != v.size()) {
       throw std::invalid_argument("mgt_get_grad: size mismatch");
     }

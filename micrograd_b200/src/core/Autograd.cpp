@@ -10,7 +10,17 @@
 #include <unordered_set>
 #include <utility>
 
+namespace micrograd::detail {
+namespace {
+unsigned long long g_backward_sweep = 0;
+}
+// Number of backward() calls started so far in this process; a grad-ready hook
+// reads it to tell one sweep from the next.
+unsigned long long backward_sweep() { return g_backward_sweep; }
+}  // namespace micrograd::detail
+
 void Tensor::backward() {
+  micrograd::detail::g_backward_sweep++;
   std::vector<Tensor *> ordered;
   std::unordered_set<Tensor *> visited;
   std::vector<std::pair<Tensor *, size_t>> stack;

@@ -19,6 +19,12 @@ void check(int rc, const char *what) {
 }
 
 Storage::~Storage() {
+  if (mg_device() < 0) {
+    // The device context is gone (mg_shutdown, or static destruction order at
+    // exit): its pool and events went with it, and touching the ABI here would
+    // bring a whole new context up only to fail the lookups.
+    return;
+  }
   if (pending_upload_ >= 0) {
     // never read: still order the free after the copy
     mg_compute_wait_event(pending_upload_);
@@ -84,7 +90,17 @@ void Storage::sync_device_from_host() {
   dev_valid_ = true;
 }
 
+void Storage::settle_exchange() {
+  if (comm_pending_) {
+    // An all-reduce on the communication stream is still writing this buffer (peers
+    // store into it too): reads on the compute stream wait for it on the device.
+    check(mg_comm_join(), "comm join");
+    comm_pending_ = false;
+  }
+}
+
 void Storage::sync_host_from_device() {
+  settle_exchange();
   host_.resize(size_);
   double mirrored = 0.0;
   if (fetch_mirror(&mirrored)) {
@@ -185,6 +201,10 @@ void Storage::fill(double value) {
 
 std::vector<double> &Storage::host_mutable() {
   host_const();  // (before the stamp moves: a pending scalar mirror is still current here)
+  if (zero_) {
+    zero_ = false;  // the zeros just written to host_ are now the contents
+    host_valid_ = true;
+  }
   write_stamp_++;
   // The caller may write through the reference at any later time, so the host
   // vector is the authority until a kernel needs the values again.
@@ -195,10 +215,9 @@ std::vector<double> &Storage::host_mutable() {
 const std::vector<double> &Storage::host_const() {
   settle_upload();
   if (zero_) {
+    // A read does not end the logical-zero state: the next accumulation is still
+    // a plain store and no buffer has to be filled.
     host_.assign(size_, 0.0);
-    zero_ = false;
-    host_valid_ = true;
-    dev_valid_ = false;
   } else if (!host_valid_) {
     sync_host_from_device();
   }
@@ -217,6 +236,7 @@ double Storage::peek(size_t index) {
   if (fetch_mirror(&v)) {
     return v;
   }
+  settle_exchange();
   check(mg_download(&v, dev_ + index, 1), "download");
   return v;
 }

@@ -81,6 +81,10 @@ std::vector<double> &Tensor::data() { return data_.host_mutable(); }
 
 std::vector<double> &Tensor::grad() { return grad_.host_mutable(); }
 
+const std::vector<double> &Tensor::data() const { return data_.host_const(); }
+
+const std::vector<double> &Tensor::grad() const { return grad_.host_const(); }
+
 // Reference: loop writing 0.0 (Tensor.cpp:73-77).  Here the gradient returns to
 // the logical-zero state, so the next accumulation is a plain store.
 void Tensor::zero_grad() { grad_.set_zero(); }

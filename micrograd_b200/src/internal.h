@@ -9,6 +9,8 @@
 #include "micrograd/Tensor.h"
 
 namespace micrograd::detail {
+unsigned long long backward_sweep();  // Autograd.cpp: backward() calls started so far
+
 struct TensorAccess {
   static Storage &data(Tensor &t) { return t.data_; }
   static Storage &grad(Tensor &t) { return t.grad_; }

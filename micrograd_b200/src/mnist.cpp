@@ -1,7 +1,9 @@
 // IDX file reader (reference: src/mnist.cpp).  Same file handling as the
 // reference — 16-byte image header and 8-byte label header are skipped, one
 // byte per pixel scaled by 1/255, one byte per label — but the files are read
-// with two block reads and the data reach the GPU in two uploads.
+// with two block reads, the pixel bytes are uploaded as bytes and divided by
+// 255.0 on the device (one IEEE division per pixel, the same value the host
+// computes), and the labels follow in a second upload.
 #include "micrograd/mnist.h"
 
 #include <fstream>
@@ -15,7 +17,7 @@ using micrograd::detail::check;
 namespace {
 
 struct RawMnist {
-  std::vector<double> pixels;  // [count][784], already divided by 255
+  std::vector<unsigned char> pixels;  // [count][784], raw bytes
   std::vector<unsigned char> labels;
 };
 
@@ -24,7 +26,8 @@ RawMnist read_idx(const std::string &images_path, const std::string &labels_path
   const size_t count = sample_count > 0 ? static_cast<size_t>(sample_count) : 0;
   std::ifstream images(images_path, std::ios::binary);
   std::ifstream labels(labels_path, std::ios::binary);
-  std::vector<unsigned char> bytes(count * 784, 0);
+  std::vector<unsigned char> &bytes = raw.pixels;
+  bytes.assign(count * 784, 0);
   raw.labels.assign(count, 0);
   // Like the reference, a missing or short file is not an error: unread samples
   // keep zero pixels and label 0.
@@ -36,10 +39,6 @@ RawMnist read_idx(const std::string &images_path, const std::string &labels_path
     labels.seekg(8);
     labels.read(reinterpret_cast<char *>(raw.labels.data()),
                 static_cast<std::streamsize>(raw.labels.size()));
-  }
-  raw.pixels.resize(bytes.size());
-  for (size_t i = 0; i < bytes.size(); i++) {
-    raw.pixels[i] = bytes[i] / 255.0;
   }
   return raw;
 }
@@ -67,7 +66,7 @@ MNISTData load_mnist(const std::string &images_path, const std::string &labels_p
   auto label_block = std::make_shared<DeviceBlock>();
   check(mg_alloc(count * 784, &image_block->ptr), "device allocation");
   check(mg_alloc(count * 10, &label_block->ptr), "device allocation");
-  check(mg_upload(image_block->ptr, raw.pixels.data(), count * 784), "upload");
+  check(mg_upload_u8_scaled(image_block->ptr, raw.pixels.data(), count * 784, 255.0), "upload");
   check(mg_upload(label_block->ptr, one_hot.data(), count * 10), "upload");
   data.images.reserve(count);
   data.labels.reserve(count);
@@ -91,7 +90,12 @@ MNISTBatch load_mnist_batched(const std::string &images_path, const std::string 
     ids[i] = static_cast<double>(raw.labels[i]);
   }
   MNISTBatch batch;
-  batch.images = std::make_shared<Tensor>(std::vector<size_t>{count, 784}, std::move(raw.pixels));
+  batch.images = std::make_shared<Tensor>(std::vector<size_t>{count, 784});
+  if (count > 0) {
+    check(mg_upload_u8_scaled(micrograd::detail::TensorAccess::data(*batch.images).device_overwrite(),
+                              raw.pixels.data(), count * 784, 255.0),
+          "upload");
+  }
   batch.labels = std::make_shared<Tensor>(std::vector<size_t>{count}, std::move(ids));
   return batch;
 }

@@ -8,12 +8,15 @@
 #include <fstream>
 #include <random>
 #include <stdexcept>
+#include <string>
 
 #include "internal.h"
 #include "mg_cuda.h"
 
 using micrograd::detail::check;
 using micrograd::detail::DeviceInts;
+
+using micrograd::detail::Storage;
 
 using Access = micrograd::detail::TensorAccess;
 
@@ -158,17 +161,43 @@ SGD::~SGD() {
 }
 
 void SGD::zero_grad() {
+  if (allreduce_ && buckets_.any_reduced()) {
+    // An exchange may still be writing the gradient buffer: order the next
+    // writer (the first accumulation of the coming sweep) behind it.
+    check(mg_comm_join(), "comm join");
+  }
   for (auto &p : parameters_) {
+    Access::grad(*p).set_exchange_pending(false);
     p->zero_grad();
   }
-  std::fill(ready_.begin(), ready_.end(), 0);
+  buckets_.end_step();
 }
 
 // p -= lr * g elementwise (nn.cpp:71-77), on the device.  A parameter whose
 // gradient is still logically zero is left alone (p - lr*0 == p).
 void SGD::step() {
   if (allreduce_) {
+    // A bounded wait that ran out in an earlier exchange (a rank that never
+    // joined) leaves a fault code; the copy read here was made behind the
+    // previous step's exchange, so no device synchronisation is needed.  Applying
+    // unreduced gradients would let the ranks drift apart silently.
+    int fault = 0;
+    check(mg_kernel_status_peek(&fault), "kernel status");
+    if (fault != 0) {
+      mg_check_kernel_status();  // synchronises, clears the word, records the message
+      throw std::runtime_error(std::string("SGD::step: gradient exchange failed: ") + mg_last_error());
+    }
+    // Buckets the backward sweep did not complete (a parameter outside the graph,
+    // or halves finished in different sweeps) are exchanged now: every rank takes
+    // the same decision, and no rank applies a local-only gradient.
+    for (size_t b : buckets_.unreduced()) {
+      reduce_bucket(b);
+    }
     check(mg_comm_join(), "comm join");
+    check(mg_kernel_status_mirror(), "kernel status");
+    for (auto &p : parameters_) {
+      Access::grad(*p).set_exchange_pending(false);
+    }
   }
   bool flat = flat_data_ != nullptr;
   if (flat) {
@@ -199,7 +228,7 @@ void SGD::step() {
                             learning_rate_),
           "sgd step");
   }
-  std::fill(ready_.begin(), ready_.end(), 0);
+  buckets_.end_step();
 }
 
 namespace {
@@ -251,29 +280,48 @@ void SGD::enable_allreduce() {
     Access::grad(p).rehome(flat_grad_ + offsets_[i], flat);
     Access::hook(p) = [this, i](Tensor &) { on_grad_ready(i); };
   }
-  ready_.assign(parameters_.size(), 0);
+  std::vector<std::vector<size_t>> shapes;
+  for (auto &p : parameters_) {
+    shapes.push_back(p->shape());
+  }
+  buckets_.plan(shapes, offsets_, requires_flags(), flat_elems_);
   allreduce_ = micrograd::comm_world() > 1;
 }
 
+std::vector<char> SGD::requires_flags() const {
+  std::vector<char> flags;
+  for (auto &p : parameters_) {
+    flags.push_back(p->requires_grad() ? 1 : 0);
+  }
+  return flags;
+}
+
 // Called from backward() when parameter `index` has received its last
-// contribution.  Parameters are exchanged in (weight, bias) pairs — one message
-// per layer — as soon as both halves are final, on the communication stream.
+// contribution of the sweep.  A bucket is exchanged on the communication stream
+// as soon as all its members that require a gradient are final.
 void SGD::on_grad_ready(size_t index) {
   if (!allreduce_) {
     return;
   }
-  ready_[index] = 1;
-  const size_t lo = index & ~static_cast<size_t>(1);
-  const size_t hi = std::min(lo + 1, parameters_.size() - 1);
-  if (!ready_[lo] || !ready_[hi]) {
-    return;
+  const unsigned long long sweep = micrograd::detail::backward_sweep();
+  if (buckets_.is_new_sweep(sweep)) {
+    buckets_.begin_sweep(sweep, requires_flags());
   }
-  for (size_t i = lo; i <= hi; i++) {
-    Access::grad(*parameters_[i]).device_update();  // logical zeros become real zeros
+  const long bucket = buckets_.on_ready(index);
+  if (bucket >= 0) {
+    reduce_bucket(static_cast<size_t>(bucket));
   }
-  const size_t begin = offsets_[lo];
-  const size_t end = (hi + 1 < parameters_.size()) ? offsets_[hi + 1] : flat_elems_;
-  check(mg_allreduce_sum_async(flat_grad_ + begin, end - begin), "gradient all-reduce");
+}
+
+void SGD::reduce_bucket(size_t bucket) {
+  const auto &b = buckets_.buckets()[bucket];
+  for (size_t i = b.first; i <= b.last; i++) {
+    Storage &g = Access::grad(*parameters_[i]);
+    g.device_update();  // logical zeros become real zeros
+    g.set_exchange_pending(true);
+  }
+  check(mg_allreduce_sum_async(flat_grad_ + b.begin, b.end - b.begin), "gradient all-reduce");
+  buckets_.mark_reduced(bucket);
 }
 
 // ---------------------------------------------------------------------------

@@ -16,10 +16,12 @@ Two libraries sit behind it (built by ``oracle/Makefile``):
   and fast enough for full-size parity.  ``fast``.
 
 Parity status: pinned for every op the reference implements (against the
-reference's own compiled code and its test suite's known answers).  For the ops
-the reference lacks — ``exp``, row-broadcast add, last-axis sum, softmax
-cross-entropy, argmax — the restatements in ``ref_fast.c`` are the only
-authority: parity unpinned for those.
+reference's own compiled code and its test suite's known answers), and for the
+additions that have an exact encoding in reference code: row-broadcast add and
+the column sum (``ones[B,1] @ b[1,N]``, ``ones[1,M] @ X``) and the last-axis sum
+(``X @ ones[N,1]``), forward and backward.  For ``exp``, softmax cross-entropy
+and argmax the reference offers nothing to run; the restatements in
+``ref_fast.c`` are the only authority: parity unpinned for those three.
 """
 from __future__ import annotations
 
@@ -53,8 +55,8 @@ def ref_true():
         if not os.path.exists(REF_TRUE_PATH):
             raise FileNotFoundError(
                 f"{REF_TRUE_PATH} is missing: run `make -C oracle` where the reference tree is mounted")
-        from micrograd_b200.tensor_api import bind
-        _ref_true_ns = bind(REF_TRUE_PATH)
+        from . import ref_binding
+        _ref_true_ns = ref_binding.load(REF_TRUE_PATH)
     return _ref_true_ns
 
 

@@ -102,6 +102,31 @@ def matmul_cases(api, rng):
     return out
 
 
+def axis_sum_cases(api, rng):
+    """Encodings of two ops the reference lacks, run by the reference's own matmul
+    loop (src/ops/Matmul.cpp:30-58): the last-axis sum of X is X.matmul(ones[N,1])
+    (0.0 + x*1.0 left to right along the row) and the column sum is
+    ones[1,M].matmul(X) (ascending rows).  Their backward closures give the
+    gradients of the two sums: gx[i,j] += g[i] and gx[i,j] += g[j]."""
+    out = {}
+    M, N = 37, 23
+    X = rng.standard_normal((M, N))
+    gx0 = rng.standard_normal((M, N))
+    seed_rows, seed_cols = rng.standard_normal((M, 1)), rng.standard_normal((1, N))
+    tx, ones = api.Tensor([M, N], X), api.Tensor([N, 1], np.ones(N))
+    tx.set_grad(gx0)
+    rows = tx.matmul(ones)
+    rows.mul(api.Tensor([M, 1], seed_rows)).sum().backward()
+    out.update(X=X, gx0=gx0, seed_rows=seed_rows.reshape(M), seed_cols=seed_cols.reshape(N),
+               row_sums=rows.data().reshape(M), row_sums_gx=tx.grad().reshape(M, N))
+    tx, ones = api.Tensor([M, N], X), api.Tensor([1, M], np.ones(M))
+    tx.set_grad(gx0)
+    cols = ones.matmul(tx)
+    cols.mul(api.Tensor([1, N], seed_cols)).sum().backward()
+    out.update(col_sums=cols.data().reshape(N), col_sums_gx=tx.grad().reshape(M, N))
+    return out
+
+
 def mse_case(api, rng):
     pred = rng.standard_normal((1, 10))
     target = np.zeros((1, 10))
@@ -190,6 +215,8 @@ def main():
     np.savez(os.path.join(HERE, "mse.npz"), **mse_case(api, rng))
     np.savez(os.path.join(HERE, "mlp_c1.npz"), **mlp_case(rng))
     np.savez(os.path.join(HERE, "trainer_mnist_bin.npz"), **trainer_cases(api, rng))
+    # separate generator: adding cases must not shift the stream the files above were drawn from
+    np.savez(os.path.join(HERE, "axis_sums.npz"), **axis_sum_cases(api, np.random.default_rng(20240612)))
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")

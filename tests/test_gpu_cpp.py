@@ -1,6 +1,6 @@
 """GPU: C++-level drop-in checks.
 
-``oracle/_ref/tensor_test_b200`` is the reference project's own
+``tests/cpp/bin/tensor_test_b200`` is the reference project's own
 test/tensor_test.cpp, compiled without modification against this repository's
 headers and linked with the B200 backend (built where the reference tree is
 mounted).  ``tests/cpp/bin/api_test`` is this repository's own C++ test file.
@@ -23,7 +23,7 @@ def _run(path):
 
 
 def test_reference_test_file_runs_unchanged_on_b200_backend():
-    out = _run(os.path.join(ROOT, "oracle", "_ref", "tensor_test_b200"))
+    out = _run(os.path.join(ROOT, "tests", "cpp", "bin", "tensor_test_b200"))
     assert "11 tests ran" in out and "[  PASSED  ] 11 tests" in out
 
 
