@@ -251,6 +251,11 @@ int mg_comm_destroy(void);
 int mg_comm_rank(void);
 int mg_comm_world(void);
 int mg_allreduce_sum_async(double *buf, size_t n);
+/* The same with a hint.  exposed != 0: the caller will wait for this exchange with
+ * nothing left to overlap it (the last gradient message of a backward pass), so
+ * the peer-memory kernel may spread over most of the SMs; exposed == 0 keeps it on
+ * a few SMs so the GEMMs it overlaps lose little.  All ranks pass the same hint. */
+int mg_allreduce_sum_async_hint(double *buf, size_t n, int exposed);
 /* Collective over the communicator (every rank calls it, in the same order, with
  * the same n): a zero-filled device buffer of n doubles that every rank maps
  * through CUDA IPC.  If any rank cannot map any peer, every rank keeps a plain
@@ -262,6 +267,14 @@ int mg_comm_free_shared(double *ptr);
  * kernel; with ptr == NULL, 1 if any live shared buffer does. */
 int mg_comm_peer_path(const double *ptr);
 int mg_comm_join(void); /* compute stream waits for all all-reduces enqueued so far */
+/* Timing of the exchange, off by default.  While enabled, every all-reduce is
+ * bracketed by an event pair on the communication stream and every mg_comm_join()
+ * by a pair on the compute stream.  mg_comm_trace_summary() waits for both
+ * streams, returns the summed duration of the all-reduces and the summed time the
+ * compute stream spent waiting in joins (the part of the exchange that compute
+ * did not hide), with their counts, and starts a new collection. */
+int mg_comm_trace(int enable);
+int mg_comm_trace_summary(double *exchange_ms, int *exchanges, double *exposed_ms, int *joins);
 /* Polls NCCL's async error state and the comm stream up to timeout_s; aborts
  * the communicator and returns MG_ERR_TIMEOUT / MG_ERR_NCCL on failure. */
 int mg_comm_wait_bounded(double timeout_s);
@@ -271,6 +284,12 @@ int mg_comm_wait_bounded(double timeout_s);
  * register operands only; writes achieved TFLOP/s.  shape: 0 m8n8k4, 1 m16n8k4,
  * 2 m16n8k8, 3 m16n8k16. */
 int mg_probe_dmma_tflops(int shape, int iters, double *tflops_host);
+/* Synthetic uniform [0,1) inputs made on the device (no counterpart in the
+ * reference, which reads its inputs from MNIST files): dst[i] is a pure function
+ * of seed and first_index + i (splitmix64, top 53 bits), so a row shard of a large
+ * input is generated on the GPU that uses it and the same values can be recomputed
+ * on the host for checking. */
+int mg_fill_uniform01(double *dst, size_t n, unsigned long long seed, unsigned long long first_index);
 /* Overwrites a buffer larger than L2 so the next timed launch starts cold. */
 int mg_flush_l2(void);
 /* Count of kernel launches issued by this library since process start. */

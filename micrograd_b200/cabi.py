@@ -96,12 +96,16 @@ SIGNATURES = {
     "mg_comm_rank": (C.c_int, []),
     "mg_comm_world": (C.c_int, []),
     "mg_allreduce_sum_async": (C.c_int, [C.c_void_p, _sz]),
+    "mg_allreduce_sum_async_hint": (C.c_int, [C.c_void_p, _sz, C.c_int]),
     "mg_comm_alloc_shared": (C.c_int, [_sz, C.POINTER(C.c_void_p)]),
     "mg_comm_free_shared": (C.c_int, [C.c_void_p]),
     "mg_comm_peer_path": (C.c_int, [C.c_void_p]),
     "mg_comm_join": (C.c_int, []),
+    "mg_comm_trace": (C.c_int, [C.c_int]),
+    "mg_comm_trace_summary": (C.c_int, [_dp, _ip, _dp, _ip]),
     "mg_comm_wait_bounded": (C.c_int, [C.c_double]),
     "mg_probe_dmma_tflops": (C.c_int, [C.c_int, C.c_int, _dp]),
+    "mg_fill_uniform01": (C.c_int, [C.c_void_p, _sz, C.c_ulonglong, C.c_ulonglong]),
     "mg_flush_l2": (C.c_int, []),
     "mg_launch_count": (C.c_ulonglong, []),
 }

@@ -25,6 +25,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <thread>
+#include <utility>
 #include <vector>
 
 namespace mg {
@@ -113,6 +114,27 @@ struct SharedBuffer {
 };
 
 std::vector<SharedBuffer> g_shared;
+
+// Optional timing of the exchange (mg_comm_trace): event pairs around every
+// all-reduce on the communication stream, and around every point where the
+// compute stream waits for that stream (the part of the exchange that is NOT
+// hidden behind compute).  Off by default; nothing is recorded then.
+struct CommTrace {
+  bool on = false;
+  std::vector<cudaEvent_t> pool;  // events handed out in order, reused after a summary
+  size_t next = 0;
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> exchanges, waits;
+};
+CommTrace g_trace;
+
+cudaEvent_t trace_event() {
+  if (g_trace.next == g_trace.pool.size()) {
+    cudaEvent_t ev = nullptr;
+    if (cudaEventCreate(&ev) != cudaSuccess) return nullptr;
+    g_trace.pool.push_back(ev);
+  }
+  return g_trace.pool[g_trace.next++];
+}
 
 struct PeerArgs {
   double *data[kMaxPeers];     // every rank's buffer, indexed by rank
@@ -261,8 +283,11 @@ SharedBuffer *find_shared(const double *buf, size_t n) {
   return nullptr;
 }
 
+// `exposed`: nothing else will be running beside this exchange (the caller is
+// about to wait for it), so it may spread over most of the GPU instead of the few
+// SMs an exchange that hides behind GEMMs should take from them.
 template <int W>
-int launch_peer_allreduce(SharedBuffer &b, size_t offset, size_t n) {
+int launch_peer_allreduce(SharedBuffer &b, size_t offset, size_t n, bool exposed) {
   Context &c = ctx();
   PeerArgs a;
   for (int q = 0; q < kMaxPeers; q++) {
@@ -278,7 +303,12 @@ int launch_peer_allreduce(SharedBuffer &b, size_t offset, size_t n) {
   const size_t words_per_rank = (n / 2 + W - 1) / W;
   size_t ctas = (words_per_rank + 2 * kPeerThreads - 1) / (2 * kPeerThreads);
   if (ctas < 1) ctas = 1;
-  if (ctas > (size_t)peer_ctas()) ctas = (size_t)peer_ctas();
+  size_t cap = (size_t)peer_ctas();
+  if (exposed) {
+    const size_t wide = (size_t)(c.sm_count > 20 ? c.sm_count - 20 : c.sm_count);
+    if (wide > cap) cap = wide;
+  }
+  if (ctas > cap) ctas = cap;
   peer_allreduce_kernel<W><<<(unsigned)ctas, kPeerThreads, 0, c.comm_stream>>>(a);
   MG_LAUNCH_CHECK("peer_allreduce");
   return MG_OK;
@@ -362,7 +392,9 @@ int mg_comm_destroy(void) {
 int mg_comm_rank(void) { return g_rank; }
 int mg_comm_world(void) { return g_world; }
 
-int mg_allreduce_sum_async(double *buf, size_t n) {
+int mg_allreduce_sum_async(double *buf, size_t n) { return mg_allreduce_sum_async_hint(buf, n, 0); }
+
+int mg_allreduce_sum_async_hint(double *buf, size_t n, int exposed) {
   MG_ENSURE_INIT();
   if (n == 0) return MG_OK;
   if (!buf) return fail(MG_ERR_INVALID, "mg_allreduce_sum_async: null buffer");
@@ -374,22 +406,34 @@ int mg_allreduce_sum_async(double *buf, size_t n) {
   // comm stream picks up after everything enqueued on the compute stream so far
   MG_CUDA_TRY(cudaEventRecord(c.fork_event, c.stream));
   MG_CUDA_TRY(cudaStreamWaitEvent(c.comm_stream, c.fork_event, 0));
+  cudaEvent_t t0 = nullptr, t1 = nullptr;
+  if (g_trace.on && (t0 = trace_event()) && (t1 = trace_event()))
+    MG_CUDA_TRY(cudaEventRecord(t0, c.comm_stream));
+  int rc = MG_OK;
+  bool launched = false;
   // The choice below depends only on values that are equal on every rank.
   SharedBuffer *shared = find_shared(buf, n);
   if (shared && shared->peers_mapped && !peer_path_disabled()) {
     const size_t offset = (size_t)(buf - shared->base);
     if (((offset | n) & 1) == 0) {
+      launched = true;
       switch (g_world) {
-        case 2: return launch_peer_allreduce<2>(*shared, offset, n);
-        case 4: return launch_peer_allreduce<4>(*shared, offset, n);
-        case 8: return launch_peer_allreduce<8>(*shared, offset, n);
-        default: break;
+        case 2: rc = launch_peer_allreduce<2>(*shared, offset, n, exposed != 0); break;
+        case 4: rc = launch_peer_allreduce<4>(*shared, offset, n, exposed != 0); break;
+        case 8: rc = launch_peer_allreduce<8>(*shared, offset, n, exposed != 0); break;
+        default: launched = false; break;
       }
     }
   }
-  ncclResult_t r = g_nccl.AllReduce(buf, buf, n, ncclDouble, ncclSum, g_comm, c.comm_stream);
-  if (r != ncclSuccess) return nccl_fail(r, "ncclAllReduce");
-  return MG_OK;
+  if (!launched) {
+    ncclResult_t r = g_nccl.AllReduce(buf, buf, n, ncclDouble, ncclSum, g_comm, c.comm_stream);
+    if (r != ncclSuccess) return nccl_fail(r, "ncclAllReduce");
+  }
+  if (rc == MG_OK && t0 && t1) {
+    MG_CUDA_TRY(cudaEventRecord(t1, c.comm_stream));
+    g_trace.exchanges.emplace_back(t0, t1);
+  }
+  return rc;
 }
 
 int mg_comm_alloc_shared(size_t n, double **out) {
@@ -506,8 +550,49 @@ int mg_comm_peer_path(const double *ptr) {
 int mg_comm_join(void) {
   MG_ENSURE_INIT();
   Context &c = ctx();
+  cudaEvent_t t0 = nullptr, t1 = nullptr;
+  if (g_trace.on && (t0 = trace_event()) && (t1 = trace_event()))
+    MG_CUDA_TRY(cudaEventRecord(t0, c.stream));
   MG_CUDA_TRY(cudaEventRecord(c.join_event, c.comm_stream));
   MG_CUDA_TRY(cudaStreamWaitEvent(c.stream, c.join_event, 0));
+  if (t0 && t1) {
+    MG_CUDA_TRY(cudaEventRecord(t1, c.stream));
+    g_trace.waits.emplace_back(t0, t1);
+  }
+  return MG_OK;
+}
+
+int mg_comm_trace(int enable) {
+  MG_ENSURE_INIT();
+  g_trace.on = enable != 0;
+  return MG_OK;
+}
+
+int mg_comm_trace_summary(double *exchange_ms, int *exchanges, double *exposed_ms, int *joins) {
+  MG_ENSURE_INIT();
+  if (!exchange_ms || !exchanges || !exposed_ms || !joins)
+    return fail(MG_ERR_INVALID, "mg_comm_trace_summary: null pointer");
+  Context &c = ctx();
+  MG_CUDA_TRY(cudaStreamSynchronize(c.stream));
+  MG_CUDA_TRY(cudaStreamSynchronize(c.comm_stream));
+  double ex = 0.0, wt = 0.0;
+  for (auto &p : g_trace.exchanges) {
+    float ms = 0.f;
+    MG_CUDA_TRY(cudaEventElapsedTime(&ms, p.first, p.second));
+    ex += ms;
+  }
+  for (auto &p : g_trace.waits) {
+    float ms = 0.f;
+    MG_CUDA_TRY(cudaEventElapsedTime(&ms, p.first, p.second));
+    wt += ms;
+  }
+  *exchange_ms = ex;
+  *exchanges = (int)g_trace.exchanges.size();
+  *exposed_ms = wt;
+  *joins = (int)g_trace.waits.size();
+  g_trace.exchanges.clear();
+  g_trace.waits.clear();
+  g_trace.next = 0;
   return MG_OK;
 }
 

@@ -58,6 +58,8 @@ int ensure_scratch(double **buf, size_t *have, size_t elems);
 
 // Frees the segment tables the GEMM dispatcher caches on the device.
 void gemm_release_tables();
+// Clears the arrival counters of split-contraction tiles (after a kernel fault).
+void gemm_reset_tickets();
 
 inline void count_launch() { ctx().launches++; }
 
@@ -79,6 +81,26 @@ inline void count_launch() { ctx().launches++; }
     cudaError_t mg_e_ = cudaGetLastError();                                                        \
     if (mg_e_ != cudaSuccess) return ::mg::cuda_fail(mg_e_, name);                                 \
   } while (0)
+
+// 32-byte vector of four doubles: sm_100 has 256-bit global loads and stores
+// (ld/st.global.v4.f64).  The streaming forms keep once-touched data out of L1.
+struct __align__(32) double4v {
+  double x, y, z, w;
+};
+#ifdef __CUDACC__
+__device__ __forceinline__ double4v ld_stream_v4(const double4v *p) {
+  double4v v;
+  asm volatile("ld.global.cs.v4.f64 {%0,%1,%2,%3}, [%4];"
+               : "=d"(v.x), "=d"(v.y), "=d"(v.z), "=d"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_stream_v4(double4v *p, double4v v) {
+  asm volatile("st.global.cs.v4.f64 [%0], {%1,%2,%3,%4};" ::"l"(p), "d"(v.x), "d"(v.y), "d"(v.z),
+               "d"(v.w)
+               : "memory");
+}
+#endif
 
 // Grid for a grid-stride kernel over `work_items` with `threads` per CTA:
 // enough CTAs to cover the work, capped at `ctas_per_sm` resident CTAs per SM

@@ -115,6 +115,22 @@ int ensure_scratch(double **buf, size_t *have, size_t elems) {
 
 using namespace mg;
 
+// Registers a new event under the smallest free id.
+static int create_event(unsigned flags, int *out_id) {
+  cudaEvent_t ev;
+  MG_CUDA_TRY(cudaEventCreateWithFlags(&ev, flags));
+  for (size_t i = 0; i < g_events.size(); i++) {
+    if (!g_events[i]) {
+      g_events[i] = ev;
+      *out_id = (int)i;
+      return MG_OK;
+    }
+  }
+  g_events.push_back(ev);
+  *out_id = (int)g_events.size() - 1;
+  return MG_OK;
+}
+
 extern "C" {
 
 const char *mg_last_error(void) { return t_last_error.c_str(); }
@@ -183,6 +199,7 @@ int mg_check_kernel_status(void) {
   if (status != 0) {
     cudaMemsetAsync(g_ctx.kernel_status, 0, sizeof(int), g_ctx.stream);
     if (g_ctx.status_host) *g_ctx.status_host = 0;
+    gemm_reset_tickets();
     return fail(MG_ERR_KERNEL, "a kernel raised fault code %d (bounded wait expired or bad geometry)",
                 status);
   }
@@ -264,8 +281,9 @@ int mg_upload_async(double *dst, const double *src_host, size_t n, int *out_even
   if (n)
     MG_CUDA_TRY(cudaMemcpyAsync(dst, src_host, n * sizeof(double), cudaMemcpyHostToDevice,
                                 c.copy_stream));
+  // Ordering only: an event without timing is cheaper to record and to wait on.
   int id = -1;
-  int rc = mg_event_create(&id);
+  int rc = create_event(cudaEventDisableTiming, &id);
   if (rc != MG_OK) return rc;
   MG_CUDA_TRY(cudaEventRecord(g_events[id], c.copy_stream));
   *out_event_id = id;
@@ -409,18 +427,7 @@ int mg_host_free(void *host) {
 int mg_event_create(int *out_id) {
   MG_ENSURE_INIT();
   if (!out_id) return fail(MG_ERR_INVALID, "mg_event_create: null out pointer");
-  cudaEvent_t ev;
-  MG_CUDA_TRY(cudaEventCreate(&ev));
-  for (size_t i = 0; i < g_events.size(); i++) {
-    if (!g_events[i]) {
-      g_events[i] = ev;
-      *out_id = (int)i;
-      return MG_OK;
-    }
-  }
-  g_events.push_back(ev);
-  *out_id = (int)g_events.size() - 1;
-  return MG_OK;
+  return create_event(cudaEventDefault, out_id);
 }
 
 static int event_at(int id, cudaEvent_t *ev) {

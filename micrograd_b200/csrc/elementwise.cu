@@ -18,16 +18,12 @@ namespace mg {
 
 constexpr int kEwThreads = 256;
 constexpr int kEwUnroll = 4;
-constexpr int kEwCtasPerSm = 8;
+constexpr int kEwWaves = 16;
 
 template <int VEC> struct VecT;
 template <> struct VecT<2> {
   using type = double2;
   static __device__ __forceinline__ double2 zero() { return make_double2(0.0, 0.0); }
-};
-// 32-byte vector: sm_100 has 256-bit global loads and stores (ld/st.global.v4.f64).
-struct __align__(32) double4v {
-  double x, y, z, w;
 };
 template <> struct VecT<4> {
   using type = double4v;
@@ -51,18 +47,8 @@ __device__ __forceinline__ double lane(const double4v &v, int i) {
 __device__ __forceinline__ void set_lane(double4v &v, int i, double x) {
   if (i == 0) v.x = x; else if (i == 1) v.y = x; else if (i == 2) v.z = x; else v.w = x;
 }
-__device__ __forceinline__ double4v ld_stream(const double4v *p) {
-  double4v v;
-  asm volatile("ld.global.cs.v4.f64 {%0,%1,%2,%3}, [%4];"
-               : "=d"(v.x), "=d"(v.y), "=d"(v.z), "=d"(v.w)
-               : "l"(p));
-  return v;
-}
-__device__ __forceinline__ void st_stream(double4v *p, double4v v) {
-  asm volatile("st.global.cs.v4.f64 [%0], {%1,%2,%3,%4};" ::"l"(p), "d"(v.x), "d"(v.y), "d"(v.z),
-               "d"(v.w)
-               : "memory");
-}
+__device__ __forceinline__ double4v ld_stream(const double4v *p) { return ld_stream_v4(p); }
+__device__ __forceinline__ void st_stream(double4v *p, double4v v) { st_stream_v4(p, v); }
 
 // Streaming loads/stores: every element is touched once, so keep it out of L1.
 template <class V> __device__ __forceinline__ V ld_stream(const V *p) { return __ldcs(p); }
@@ -137,19 +123,40 @@ template <class F> static uintptr_t pointer_bits(const F &f) {
   return bits;
 }
 
+// Grid of a streaming kernel: up to kEwWaves times the CTAs that are resident at
+// once (occupancy of this very instantiation x SM count), never more than the
+// work needs.  Measured on B200 (1R+1W, 2R+1W and read-modify-write maps, 2^24 to
+// 2^28 elements, waves = 1, 2, 3, 4, 6, 8, 16, 64): a grid of exactly one
+// resident wave is the slowest choice — relu at 2^24 elements 5.39 TB/s with one
+// wave, 5.66 with two, 5.99 with four, 6.12 with sixteen; at 2^26 5.87 / 6.14 /
+// 6.42 / 6.61 — because SMs do not stream at equal speed and the hardware
+// scheduler can only even that out while it has CTAs left to hand out.  Beyond
+// sixteen the one-input maps fall off again (the loop degenerates to one vector
+// per thread), so sixteen it is.
+template <class Kernel> static int resident_ctas_per_sm(Kernel kernel, int threads) {
+  int n = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n < 1) {
+    cudaGetLastError();
+    n = 1;
+  }
+  return n;
+}
+
+template <int VEC, class F> static unsigned map_grid(size_t n) {
+  static const int resident = resident_ctas_per_sm(map_kernel<VEC, F>, kEwThreads);
+  return grid_for((n + VEC - 1) / VEC, kEwThreads, resident * kEwWaves);
+}
+
 template <class F> static int launch_map(const F &f, size_t n, const char *name) {
   if (n == 0) return MG_OK;
   Context &c = ctx();
   const uintptr_t bits = pointer_bits(f);
   if ((bits & 31) == 0 && n >= 4096) {
-    unsigned grid = grid_for((n + 3) / 4, kEwThreads, kEwCtasPerSm);
-    map_kernel<4, F><<<grid, kEwThreads, 0, c.stream>>>(f, n);
+    map_kernel<4, F><<<map_grid<4, F>(n), kEwThreads, 0, c.stream>>>(f, n);
   } else if ((bits & 15) == 0) {
-    unsigned grid = grid_for((n + 1) / 2, kEwThreads, kEwCtasPerSm);
-    map_kernel<2, F><<<grid, kEwThreads, 0, c.stream>>>(f, n);
+    map_kernel<2, F><<<map_grid<2, F>(n), kEwThreads, 0, c.stream>>>(f, n);
   } else {
-    unsigned grid = grid_for(n, kEwThreads, kEwCtasPerSm);
-    map_kernel<1, F><<<grid, kEwThreads, 0, c.stream>>>(f, n);
+    map_kernel<1, F><<<map_grid<1, F>(n), kEwThreads, 0, c.stream>>>(f, n);
   }
   MG_LAUNCH_CHECK(name);
   return MG_OK;
@@ -307,33 +314,57 @@ struct SgdFn {
 };
 
 // ---------------------------------------------------------------------------
-// Row-broadcast add: out[r, c] = x[r, c] + row[c].  Each thread owns a flat
-// 16-byte word and advances (r, c) incrementally, so the loop has no division.
+// Row-broadcast add: out[r, c] = x[r, c] + row[c].  Each thread owns flat vectors
+// (32, 16 or 8 bytes) and advances its column incrementally, so the loop has no
+// division; two vectors are in flight per thread.  x and out may be the same
+// buffer (the in-place accumulate of sum(axis=0) backward): every thread reads
+// its own words before it writes them, and neither pointer is declared restrict.
 // ---------------------------------------------------------------------------
+constexpr int kRowUnroll = 2;
+
 template <int VEC>
 __global__ void __launch_bounds__(kEwThreads)
-add_row_kernel(const double *__restrict__ x, const double *__restrict__ row,
-               double *__restrict__ out, size_t M, size_t N) {
+add_row_kernel(const double *x, const double *__restrict__ row, double *out, size_t M, size_t N) {
   using V = typename VecT<VEC>::type;
   const size_t ncol = N / VEC;  // vectors per row
   const size_t total = M * ncol;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
-  const size_t drow = stride / ncol, dcol = stride % ncol;
+  const size_t dcol = stride % ncol;
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   size_t c = i % ncol;
   const V *xv = reinterpret_cast<const V *>(x);
   const V *rv = reinterpret_cast<const V *>(row);
   V *ov = reinterpret_cast<V *>(out);
-  (void)drow;
+  auto next_col = [&](size_t col) {
+    col += dcol;
+    return col >= ncol ? col - ncol : col;
+  };
+  for (; i + (kRowUnroll - 1) * stride < total; i += kRowUnroll * stride) {
+    V a[kRowUnroll], b[kRowUnroll];
+    size_t col = c;
+#pragma unroll
+    for (int u = 0; u < kRowUnroll; u++) {
+      a[u] = ld_stream(xv + i + u * stride);
+      b[u] = rv[col];
+      col = next_col(col);
+    }
+    c = col;
+#pragma unroll
+    for (int u = 0; u < kRowUnroll; u++) {
+      V o;
+#pragma unroll
+      for (int l = 0; l < VEC; l++) set_lane(o, l, lane(a[u], l) + lane(b[u], l));
+      st_stream(ov + i + u * stride, o);
+    }
+  }
   for (; i < total; i += stride) {
     V a = ld_stream(xv + i);
-    V b = __ldg(rv + c);
+    V b = rv[c];
     V o;
 #pragma unroll
     for (int l = 0; l < VEC; l++) set_lane(o, l, lane(a, l) + lane(b, l));
     st_stream(ov + i, o);
-    c += dcol;
-    if (c >= ncol) c -= ncol;
+    c = next_col(c);
   }
 }
 
@@ -350,7 +381,8 @@ struct ScalarBroadcastBwd {
   }
 };
 
-// Last-axis-sum backward: gx[r, c] += g[r].
+// Last-axis-sum backward: gx[r, c] += g[r].  Same walk as the row-broadcast add,
+// tracking the row as well.
 template <int VEC>
 __global__ void __launch_bounds__(kEwThreads)
 row_scalar_bwd_kernel(const double *__restrict__ g, double *__restrict__ gx, size_t M, size_t N,
@@ -363,18 +395,37 @@ row_scalar_bwd_kernel(const double *__restrict__ g, double *__restrict__ gx, siz
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   size_t r = i / ncol, c = i % ncol;
   V *gv = reinterpret_cast<V *>(gx);
+  auto advance = [&](size_t &row, size_t &col) {
+    col += dcol;
+    row += drow;
+    if (col >= ncol) {
+      col -= ncol;
+      row++;
+    }
+  };
+  for (; i + (kRowUnroll - 1) * stride < total; i += kRowUnroll * stride) {
+    V o[kRowUnroll];
+    double sc[kRowUnroll];
+#pragma unroll
+    for (int u = 0; u < kRowUnroll; u++) {
+      sc[u] = __ldg(g + r);
+      o[u] = accumulate ? ld_stream(gv + i + u * stride) : VecT<VEC>::zero();
+      advance(r, c);
+    }
+#pragma unroll
+    for (int u = 0; u < kRowUnroll; u++) {
+#pragma unroll
+      for (int l = 0; l < VEC; l++) set_lane(o[u], l, lane(o[u], l) + sc[u]);
+      st_stream(gv + i + u * stride, o[u]);
+    }
+  }
   for (; i < total; i += stride) {
-    const double s = __ldg(g + r);
+    const double sc = __ldg(g + r);
     V o = accumulate ? ld_stream(gv + i) : VecT<VEC>::zero();
 #pragma unroll
-    for (int l = 0; l < VEC; l++) set_lane(o, l, lane(o, l) + s);
+    for (int l = 0; l < VEC; l++) set_lane(o, l, lane(o, l) + sc);
     st_stream(gv + i, o);
-    c += dcol;
-    r += drow;
-    if (c >= ncol) {
-      c -= ncol;
-      r++;
-    }
+    advance(r, c);
   }
 }
 
@@ -486,6 +537,19 @@ __global__ void __launch_bounds__(256) sgd_multi_kernel(SgdBatch b, double lr) {
       for (; i < n; i += stride) p[i] = p[i] - lr * g[i];
     }
   }
+}
+
+// Widest vector (in doubles) that the row length and all the pointers allow.
+static int row_vector_width(size_t N, uintptr_t pointer_bits) {
+  if (N % 4 == 0 && (pointer_bits & 31) == 0) return 4;
+  if (N % 2 == 0 && (pointer_bits & 15) == 0) return 2;
+  return 1;
+}
+
+// `resident` caches the occupancy of one kernel instantiation (0 = not asked yet).
+template <class Kernel> static unsigned row_grid(Kernel kernel, size_t items, int *resident) {
+  if (*resident == 0) *resident = resident_ctas_per_sm(kernel, kEwThreads);
+  return grid_for(items, kEwThreads, *resident * kEwWaves);
 }
 
 extern "C" {
@@ -616,12 +680,16 @@ int mg_add_row_fwd(const double *x, const double *row, double *out, size_t M, si
   Context &c = ctx();
   uintptr_t bits = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(row) |
                    reinterpret_cast<uintptr_t>(out);
-  if ((N % 2 == 0) && (bits & 15) == 0) {
-    unsigned grid = grid_for(M * (N / 2), kEwThreads, kEwCtasPerSm);
-    add_row_kernel<2><<<grid, kEwThreads, 0, c.stream>>>(x, row, out, M, N);
-  } else {
-    unsigned grid = grid_for(M * N, kEwThreads, kEwCtasPerSm);
-    add_row_kernel<1><<<grid, kEwThreads, 0, c.stream>>>(x, row, out, M, N);
+  static int resident[3] = {0, 0, 0};
+  switch (row_vector_width(N, bits)) {
+    case 4:
+      add_row_kernel<4><<<row_grid(add_row_kernel<4>, M * (N / 4), &resident[2]), kEwThreads, 0, c.stream>>>(x, row, out, M, N);
+      break;
+    case 2:
+      add_row_kernel<2><<<row_grid(add_row_kernel<2>, M * (N / 2), &resident[1]), kEwThreads, 0, c.stream>>>(x, row, out, M, N);
+      break;
+    default:
+      add_row_kernel<1><<<row_grid(add_row_kernel<1>, M * N, &resident[0]), kEwThreads, 0, c.stream>>>(x, row, out, M, N);
   }
   MG_LAUNCH_CHECK("add_row_fwd");
   return MG_OK;
@@ -644,12 +712,16 @@ int mg_sum_lastaxis_bwd(const double *g, double *gx, size_t M, size_t N, int fla
   if (!g) return fail(MG_ERR_INVALID, "mg_sum_lastaxis_bwd: null upstream gradient");
   Context &c = ctx();
   const bool acc = !(flags & MG_ACC_STORE_A);
-  if ((N % 2 == 0) && (reinterpret_cast<uintptr_t>(gx) & 15) == 0) {
-    unsigned grid = grid_for(M * (N / 2), kEwThreads, kEwCtasPerSm);
-    row_scalar_bwd_kernel<2><<<grid, kEwThreads, 0, c.stream>>>(g, gx, M, N, acc);
-  } else {
-    unsigned grid = grid_for(M * N, kEwThreads, kEwCtasPerSm);
-    row_scalar_bwd_kernel<1><<<grid, kEwThreads, 0, c.stream>>>(g, gx, M, N, acc);
+  static int resident[3] = {0, 0, 0};
+  switch (row_vector_width(N, reinterpret_cast<uintptr_t>(gx))) {
+    case 4:
+      row_scalar_bwd_kernel<4><<<row_grid(row_scalar_bwd_kernel<4>, M * (N / 4), &resident[2]), kEwThreads, 0, c.stream>>>(g, gx, M, N, acc);
+      break;
+    case 2:
+      row_scalar_bwd_kernel<2><<<row_grid(row_scalar_bwd_kernel<2>, M * (N / 2), &resident[1]), kEwThreads, 0, c.stream>>>(g, gx, M, N, acc);
+      break;
+    default:
+      row_scalar_bwd_kernel<1><<<row_grid(row_scalar_bwd_kernel<1>, M * N, &resident[0]), kEwThreads, 0, c.stream>>>(g, gx, M, N, acc);
   }
   MG_LAUNCH_CHECK("sum_lastaxis_bwd");
   return MG_OK;

@@ -26,9 +26,10 @@
 //     into one equal span per SM; a span that crosses a tile boundary becomes two
 //     segments.  Every segment is one CTA; segments are issued longest first, so
 //     the hardware scheduler pairs each SM's long piece with the complementary
-//     short one and all SMs finish together.  Tiles covered by several segments
-//     are written as packed partial tiles and folded in k order by a second
-//     kernel, so the result is still reproducible.
+//     short one and all SMs finish together.  A tile covered by several segments
+//     is written as packed partial tiles; the segment that finishes last (a
+//     ticket per tile) adds them up in k order, whatever the arrival order, and
+//     runs the epilogue, so the result is reproducible and no second kernel runs.
 //   - Short work items run as a persistent grid (one CTA per SM looping over
 //     items, the producer prefetching across items); long ones as one item per
 //     CTA under the hardware scheduler.
@@ -61,7 +62,8 @@ struct TileCfg {
   static constexpr int BM = WARPS_M * MT * 16, BN = WARPS_N * NT * 8;
   static constexpr int A_BYTES = BM * BK * 8, B_BYTES = BN * BK * 8;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 2 * STAGES * 8;
+  static constexpr int SMEM_BYTES =
+      STAGES * STAGE_BYTES + 1024 /* alignment slack */ + (2 * STAGES + 1) * 8 /* barriers */;
   // The ReLU-mask source tile of an output tile, staged through the same ring
   // after the last k-tile: BN/16 boxes of BM rows x 16 columns (128-byte rows).
   static constexpr int MASK_BOXES = BN / 16, MASK_BOX_BYTES = BM * 128;
@@ -102,28 +104,6 @@ struct GemmEpilogue {
   int mode;             // MG_EPI_*
   int accumulate;       // D += instead of D =
 };
-
-__device__ __forceinline__ double2 apply_epilogue(double2 v, const GemmEpilogue &ep, size_t at,
-                                                  int col) {
-  if (ep.mode == MG_EPI_BIAS || ep.mode == MG_EPI_BIAS_RELU) {
-    v.x += __ldg(ep.aux + col);
-    v.y += __ldg(ep.aux + col + 1);
-    if (ep.mode == MG_EPI_BIAS_RELU) {
-      v.x = v.x > 0 ? v.x : 0.0;
-      v.y = v.y > 0 ? v.y : 0.0;
-    }
-  } else if (ep.mode == MG_EPI_RELU_MASK) {
-    const double2 m = *reinterpret_cast<const double2 *>(ep.aux + at);
-    v.x = v.x * (m.x > 0 ? 1.0 : 0.0);
-    v.y = v.y * (m.y > 0 ? 1.0 : 0.0);
-  }
-  if (ep.accumulate) {
-    const double2 old = *reinterpret_cast<const double2 *>(ep.D + at);
-    v.x = old.x + v.x;
-    v.y = old.y + v.y;
-  }
-  return v;
-}
 
 // Fragment pair (k = 2c, 2c+1) of the A operand for the MT row sub-tiles of a
 // warp: lo = rows g, hi = rows g + 8 of each 16-row sub-tile.
@@ -253,11 +233,14 @@ __device__ __forceinline__ bool consumer_loop(double (&acc)[Cfg::MT][Cfg::NT][4]
 struct WorkItem {
   int m0, n0, kt_begin, nkt;
   int slot;  // >= 0: write a packed partial tile into this slot; < 0: final epilogue
+  // For a segment of a split tile: the tile's first slot, its segment count and
+  // its index (which names the tile's arrival counter).
+  int first_slot, count, tile;
 };
 
 // One segment of a split contraction, as laid out by the host (32 bytes).
 struct SegItem {
-  int m0, n0, kt_begin, nkt, slot, pad0, pad1, pad2;
+  int m0, n0, kt_begin, nkt, slot, first_slot, count, tile;
 };
 
 // Work order without a segment table: whole tiles, numbered row-major, so the
@@ -273,7 +256,11 @@ __device__ __forceinline__ WorkItem decode_work(int id, int tiles_n, int KT,
     w.n0 = a.y;
     w.kt_begin = a.z;
     w.nkt = a.w;
-    w.slot = __ldg(&table[id].slot);
+    const int4 b = __ldg(reinterpret_cast<const int4 *>(table + id) + 1);
+    w.slot = b.x;
+    w.first_slot = b.y;
+    w.count = b.z;
+    w.tile = b.w;
     return w;
   }
   const int tile_m = id / tiles_n, tile_n = id - tile_m * tiles_n;
@@ -282,6 +269,9 @@ __device__ __forceinline__ WorkItem decode_work(int id, int tiles_n, int KT,
   w.kt_begin = 0;
   w.nkt = KT;
   w.slot = -1;
+  w.first_slot = 0;
+  w.count = 0;
+  w.tile = id;
   return w;
 }
 
@@ -295,22 +285,31 @@ __device__ __forceinline__ WorkItem decode_work(int id, int tiles_n, int KT,
 // MASKED: the epilogue is the ReLU mask and its source tile is staged through the
 // ring by the producer (a separate instantiation, so that the other epilogues'
 // register allocation is untouched).
-template <bool A_KCONTIG, bool B_KCONTIG, int SHAPE, bool EDGE, class Cfg, bool PERSISTENT, bool MASKED>
+// FOLD: launches of a split contraction.  Every segment of a split tile stores its
+// packed partial tile and then takes a ticket from the tile's arrival counter;
+// the segment that arrives last adds up the tile's partial tiles in slot order
+// (= k order, whatever the arrival order: the sum is reproducible) and runs the
+// final epilogue itself, so no second kernel is needed and the fold of one tile
+// overlaps the other CTAs' MMAs.
+template <bool A_KCONTIG, bool B_KCONTIG, int SHAPE, bool EDGE, class Cfg, bool PERSISTENT, bool MASKED,
+          bool FOLD>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                  const __grid_constant__ CUtensorMap mapMask, GemmEpilogue ep, int M, int N, int K,
                  int tiles_n, const SegItem *__restrict__ table, int grouped_ab, int total_items,
-                 int *status) {
+                 unsigned int *tile_tickets, int *status) {
   constexpr int BM = Cfg::BM, BN = Cfg::BN, MT = Cfg::MT, NT = Cfg::NT;
   constexpr int kStages = Cfg::STAGES, kStageBytes = Cfg::STAGE_BYTES, kTileBytes = Cfg::A_BYTES;
   extern __shared__ uint8_t smem_raw[];
   __shared__ int abort_flag_s;
+  __shared__ int fold_last_s;
   volatile int *abort_flag = &abort_flag_s;
 
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                               ~static_cast<uintptr_t>(1023));
   uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + kStages * kStageBytes);
   uint64_t *empty_bar = full_bar + kStages;
+  uint64_t *fold_bar = empty_bar + kStages;  // consumer warps meet here around the tile ticket
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int KT = (K + BK - 1) / BK;
@@ -321,6 +320,7 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
       mbar_init(smem_u32(full_bar + s), 1);
       mbar_init(smem_u32(empty_bar + s), kConsumerWarps);
     }
+    mbar_init(smem_u32(fold_bar), kConsumerWarps);
     mbar_fence_init();
   }
   __syncthreads();
@@ -400,6 +400,7 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     // half-slab uses chunk ^ 1.
     const int c0 = (t << 1) | (__popc(t) & 1);
     unsigned ring = 0;  // stages consumed by this CTA so far
+    unsigned fold_phase = 0;  // uses of fold_bar so far
 
     int id = blockIdx.x;
     do {
@@ -435,29 +436,75 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         }
         if (!mask_ok) break;
       }
-      if (active) {
-
       // ---------------- epilogue ----------------
-      // Per 16-row sub-tile: first every global load the epilogue needs (ReLU mask
-      // source, old values for accumulation) is issued, then the arithmetic, then
-      // the stores.  Interleaving load/store pairs would serialise them (a store
-      // may alias the next load as far as the compiler can tell) and turn the
-      // epilogue into a chain of exposed memory latencies.
       // A segment of a split tile stores its whole BM x BN accumulator, packed,
       // into its slot of the scratch buffer (rows and columns beyond the matrix
-      // hold zeros or are never read) and is done.  This is a branch of its own so
-      // that the final epilogue below keeps its register allocation.
+      // hold zeros or are never read).
+      bool finalize = w.slot < 0;
       if (w.slot >= 0) {
-        double *slot = ep.partial + (size_t)w.slot * (size_t)(BM * BN);
+        if (active) {
+          double *slot = ep.partial + (size_t)w.slot * (size_t)(BM * BN);
 #pragma unroll
-        for (int mt = 0; mt < MT; mt++)
+          for (int mt = 0; mt < MT; mt++)
 #pragma unroll
-          for (int h = 0; h < 2; h++)
+            for (int h = 0; h < 2; h++)
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++)
-              *reinterpret_cast<double2 *>(slot + (wm + mt * 16 + g + 8 * h) * BN + wn + nt * 8 + 2 * t) =
-                  make_double2(acc[mt][nt][2 * h], acc[mt][nt][2 * h + 1]);
-      } else {
+              for (int nt = 0; nt < NT; nt++)
+                *reinterpret_cast<double2 *>(slot + (wm + mt * 16 + g + 8 * h) * BN + wn + nt * 8 + 2 * t) =
+                    make_double2(acc[mt][nt][2 * h], acc[mt][nt][2 * h + 1]);
+        }
+        if (FOLD) {
+          // All consumer warps' stores are fenced before one thread takes the
+          // tile's ticket; the meeting point is an mbarrier with a bounded wait, so
+          // a warp that gave up earlier cannot strand the others.
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(fold_bar));
+          if (!mbar_wait_bounded(smem_u32(fold_bar), fold_phase++ & 1, abort_flag)) break;
+          if (warp == 0 && lane == 0) {
+            const unsigned prev = atomicAdd(tile_tickets + w.tile, 1u);
+            const bool last = prev == (unsigned)w.count - 1u;
+            if (last) tile_tickets[w.tile] = 0u;  // ready for the next launch (stream-ordered)
+            fold_last_s = last ? 1 : 0;
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(fold_bar));
+          if (!mbar_wait_bounded(smem_u32(fold_bar), fold_phase++ & 1, abort_flag)) break;
+          if (fold_last_s) {
+            __threadfence();
+            if (active) {
+#pragma unroll
+              for (int i = 0; i < MT; i++)
+#pragma unroll
+                for (int j = 0; j < NT; j++)
+#pragma unroll
+                  for (int r = 0; r < 4; r++) acc[i][j][r] = 0.0;
+              for (int k = 0; k < w.count; k++) {
+                const double *part = ep.partial + (size_t)(w.first_slot + k) * (size_t)(BM * BN);
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                  for (int h = 0; h < 2; h++)
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) {
+                      const double2 v = __ldcg(reinterpret_cast<const double2 *>(
+                          part + (wm + mt * 16 + g + 8 * h) * BN + wn + nt * 8 + 2 * t));
+                      acc[mt][nt][2 * h] += v.x;
+                      acc[mt][nt][2 * h + 1] += v.y;
+                    }
+              }
+            }
+            finalize = true;
+          }
+        }
+      }
+      // Final epilogue.  Per 16-row sub-tile: first every global load the epilogue
+      // needs (ReLU mask source, old values for accumulation) is issued, then the
+      // arithmetic, then the stores.  Interleaving load/store pairs would serialise
+      // them (a store may alias the next load as far as the compiler can tell) and
+      // turn the epilogue into a chain of exposed memory latencies.
+      if (active && finalize) {
+      {
       double *dst = ep.D;
       const bool use_mask = ep.mode == MG_EPI_RELU_MASK;
       const bool use_bias = !MASKED && (ep.mode == MG_EPI_BIAS || ep.mode == MG_EPI_BIAS_RELU);
@@ -562,38 +609,6 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     const long long start = clock64();
     while (clock64() - start < 2000000ll) {
     }
-  }
-}
-
-// Folds the packed partial tiles of every split output tile in k order and
-// applies the epilogue.  tile_segs[t] = (first slot, number of segments) of tile
-// t; tiles written directly by a single segment have count 0.  grid = (tiles, 4):
-// blockIdx.y takes a quarter of the tile's rows.
-__global__ void __launch_bounds__(256)
-splitk_finish_kernel(const double *__restrict__ partial, const int2 *__restrict__ tile_segs,
-                     int tiles_n, int BM, int BN, int M, int N, GemmEpilogue ep) {
-  const int2 seg = __ldg(tile_segs + blockIdx.x);
-  if (seg.y == 0) return;
-  const int tile_m = blockIdx.x / tiles_n, tile_n = blockIdx.x - tile_m * tiles_n;
-  const int words_per_row = BN >> 1;
-  const int rows_here = (BM + (int)gridDim.y - 1) / (int)gridDim.y;
-  const int r_lo = blockIdx.y * rows_here, r_hi = min(BM, r_lo + rows_here);
-  const size_t tile_elems = (size_t)BM * (size_t)BN;
-  const double *first = partial + (size_t)seg.x * tile_elems;
-  for (int idx = r_lo * words_per_row + threadIdx.x; idx < r_hi * words_per_row; idx += blockDim.x) {
-    const int r = idx / words_per_row, c = (idx - r * words_per_row) << 1;
-    const int row = tile_m * BM + r, col = tile_n * BN + c;
-    if (row >= M || col >= N) continue;
-    double2 v = make_double2(0.0, 0.0);
-    for (int k = 0; k < seg.y; k++) {
-      const double2 p =
-          __ldcs(reinterpret_cast<const double2 *>(first + (size_t)k * tile_elems + (size_t)r * BN + c));
-      v.x += p.x;
-      v.y += p.y;
-    }
-    const size_t at = (size_t)row * (size_t)N + (size_t)col;
-    v = apply_epilogue(v, ep, at, col);
-    *reinterpret_cast<double2 *>(ep.D + at) = v;
   }
 }
 
@@ -704,16 +719,17 @@ struct DmmaLaunch {
   GemmEpilogue ep;
   int M, N, K, tiles_m, tiles_n;
   const SegItem *table;  // segments of a split contraction (device), or null: whole tiles
+  unsigned int *tickets;  // arrival counters of the split tiles: fold in the kernel; null: no fold
   int items;             // CTAs' worth of work: segments, or tiles
   int min_nkt;           // shortest item, in k-tiles
   int grouped_ab;  // bit 0 / bit 1: operand A / B uses the grouped 3-D tensor map
 };
 
 
-template <bool AK, bool BK_, int SHAPE, bool EDGE, class Cfg, bool PERSISTENT, bool MASKED>
+template <bool AK, bool BK_, int SHAPE, bool EDGE, class Cfg, bool PERSISTENT, bool MASKED, bool FOLD>
 static int launch_dmma_masked(const DmmaLaunch &L) {
   static bool configured = false;
-  auto kernel = dmma_gemm_kernel<AK, BK_, SHAPE, EDGE, Cfg, PERSISTENT, MASKED>;
+  auto kernel = dmma_gemm_kernel<AK, BK_, SHAPE, EDGE, Cfg, PERSISTENT, MASKED, FOLD>;
   if (!configured) {
     MG_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      Cfg::SMEM_BYTES));
@@ -727,7 +743,7 @@ static int launch_dmma_masked(const DmmaLaunch &L) {
   dim3 grid((unsigned)((PERSISTENT && L.items > c.sm_count) ? c.sm_count : L.items), 1, 1);
   kernel<<<grid, kGemmThreads, Cfg::SMEM_BYTES, c.stream>>>(L.ma, L.mb, L.mmask, L.ep, L.M, L.N, L.K,
                                                              L.tiles_n, L.table, L.grouped_ab,
-                                                             L.items, c.kernel_status);
+                                                             L.items, L.tickets, c.kernel_status);
   MG_LAUNCH_CHECK("dmma_gemm");
   return MG_OK;
 }
@@ -737,9 +753,14 @@ static int launch_dmma_masked(const DmmaLaunch &L) {
 template <bool AK, bool BK_, int SHAPE, bool EDGE, class Cfg, bool PERSISTENT>
 static int launch_dmma_variant(const DmmaLaunch &L) {
   if constexpr (AK && BK_ && SHAPE == 2) {
-    if (L.mask_tma) return launch_dmma_masked<AK, BK_, SHAPE, EDGE, Cfg, PERSISTENT, true>(L);
+    if (L.mask_tma) return launch_dmma_masked<AK, BK_, SHAPE, EDGE, Cfg, PERSISTENT, true, false>(L);
   }
-  return launch_dmma_masked<AK, BK_, SHAPE, EDGE, Cfg, PERSISTENT, false>(L);
+  // The folding instantiation serves split contractions only: they never run
+  // persistently and read their mask (if any) with plain loads.
+  if constexpr (!PERSISTENT) {
+    if (L.tickets) return launch_dmma_masked<AK, BK_, SHAPE, EDGE, Cfg, false, false, true>(L);
+  }
+  return launch_dmma_masked<AK, BK_, SHAPE, EDGE, Cfg, PERSISTENT, false, false>(L);
 }
 
 template <bool AK, bool BK_, int SHAPE, bool EDGE, class Cfg>
@@ -882,7 +903,7 @@ struct SegTable {
   int tiles_m, tiles_n, KT, bm, bn, spans;  // key
   int items, slots, min_nkt;
   SegItem *dev_items;  // [items], longest first
-  int2 *dev_tiles;     // [tiles]: (first slot, segment count) or (0, 0) for a tile written directly
+  unsigned int *dev_tickets;  // [tiles]: arrival counters of the in-kernel fold, zero between launches
 };
 
 static std::vector<SegTable> g_seg_tables;
@@ -890,9 +911,16 @@ static std::vector<SegTable> g_seg_tables;
 void gemm_release_tables() {
   for (auto &t : g_seg_tables) {
     cudaFree(t.dev_items);
-    cudaFree(t.dev_tiles);
+    cudaFree(t.dev_tickets);
   }
   g_seg_tables.clear();
+}
+
+// After a kernel fault (a bounded wait gave up) a split tile may be left with a
+// partly counted ticket; clear them all so later launches start clean.
+void gemm_reset_tickets() {
+  for (auto &t : g_seg_tables)
+    cudaMemsetAsync(t.dev_tickets, 0, sizeof(unsigned int) * (size_t)(t.tiles_m * t.tiles_n), ctx().stream);
 }
 
 // Host-only construction of a segment table: `segs` in issue order (longest
@@ -929,6 +957,7 @@ static void build_segments(int tiles_m, int tiles_n, int KT, int bm, int bn, int
   min_nkt = KT;
   for (auto &it : segs) {
     const int tile = it.slot;
+    it.tile = tile;
     if (per_tile[(size_t)tile] > 1) {
       if (tile_info[(size_t)tile].y == 0) tile_info[(size_t)tile].x = slots;
       tile_info[(size_t)tile].y++;
@@ -937,6 +966,10 @@ static void build_segments(int tiles_m, int tiles_n, int KT, int bm, int bn, int
       it.slot = -1;
     }
     min_nkt = std::min(min_nkt, it.nkt);
+  }
+  for (auto &it : segs) {
+    it.first_slot = tile_info[(size_t)it.tile].x;
+    it.count = tile_info[(size_t)it.tile].y;
   }
   std::stable_sort(segs.begin(), segs.end(),
                    [](const SegItem &a, const SegItem &b) { return a.nkt > b.nkt; });
@@ -965,10 +998,9 @@ static int seg_table_for(int tiles_m, int tiles_n, int KT, int bm, int bn, int s
   t.slots = slots;
   t.min_nkt = min_nkt;
   MG_CUDA_TRY(cudaMalloc(&t.dev_items, segs.size() * sizeof(SegItem)));
-  MG_CUDA_TRY(cudaMalloc(&t.dev_tiles, tile_info.size() * sizeof(int2)));
+  MG_CUDA_TRY(cudaMalloc(&t.dev_tickets, tile_info.size() * sizeof(unsigned int)));
+  MG_CUDA_TRY(cudaMemset(t.dev_tickets, 0, tile_info.size() * sizeof(unsigned int)));
   MG_CUDA_TRY(cudaMemcpy(t.dev_items, segs.data(), segs.size() * sizeof(SegItem),
-                         cudaMemcpyHostToDevice));
-  MG_CUDA_TRY(cudaMemcpy(t.dev_tiles, tile_info.data(), tile_info.size() * sizeof(int2),
                          cudaMemcpyHostToDevice));
   g_seg_tables.push_back(t);
   *out = &g_seg_tables.back();
@@ -1075,6 +1107,10 @@ static int run_gemm(const GemmDesc &d) {
   L.M = M; L.N = N; L.K = K;
   L.tiles_m = tiles_m; L.tiles_n = tiles_n;
   L.table = table ? table->dev_items : nullptr;
+  // Split tiles are folded inside the kernel by their last-arriving segment.
+  const bool fold = table && table->slots > 0;
+  L.tickets = fold ? table->dev_tickets : nullptr;
+  if (fold) L.mask_tma = 0;
   L.items = table ? table->items : tiles_m * tiles_n;
   L.min_nkt = table ? table->min_nkt : KT;
   int rc;
@@ -1087,14 +1123,6 @@ static int run_gemm(const GemmDesc &d) {
   else
     return fail(MG_ERR_INVALID, "gemm: unsupported operand layout");
   if (rc != MG_OK) return rc;
-  if (table && table->slots > 0) {
-    GemmEpilogue fin = ep;
-    fin.partial = nullptr;
-    dim3 grid((unsigned)(tiles_m * tiles_n), 4, 1);
-    splitk_finish_kernel<<<grid, 256, 0, c.stream>>>(c.splitk_scratch, table->dev_tiles, tiles_n, bm,
-                                                     bn, M, N, fin);
-    MG_LAUNCH_CHECK("splitk_finish");
-  }
   return MG_OK;
 }
 

@@ -43,6 +43,24 @@ dmma_probe_kernel(int iters, double *sink) {
   if (s == 12345.678) sink[0] = s;  // never true; keeps the loop alive
 }
 
+// Synthetic inputs generated where they are used: element i of a virtual
+// stream is a pure function of (seed, i), so any shard of a large input can be
+// produced on its own GPU and reproduced on the host for checking.
+//   z = seed + (i + 1) * 0x9E3779B97F4A7C15      (splitmix64)
+//   z = (z ^ z >> 30) * 0xBF58476D1CE4E5B9 ; z = (z ^ z >> 27) * 0x94D049BB133111EB ; z ^= z >> 31
+//   value = (z >> 11) * 2^-53                    in [0, 1)
+__global__ void uniform01_kernel(double *__restrict__ dst, size_t n, unsigned long long seed,
+                                 unsigned long long first) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    unsigned long long z = seed + (first + i + 1ull) * 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    dst[i] = (double)(z >> 11) * 0x1.0p-53;
+  }
+}
+
 }  // namespace mg
 
 using namespace mg;
@@ -83,5 +101,15 @@ extern "C" int mg_probe_dmma_tflops(int shape, int iters, double *tflops_host) {
   const double warps = (double)ctas * (threads / 32);
   const double flop = warps * (double)iters * kProbeChains * flop_per_chain[shape];
   *tflops_host = flop / ((double)best_ms * 1e-3) / 1e12;
+  return MG_OK;
+}
+
+extern "C" int mg_fill_uniform01(double *dst, size_t n, unsigned long long seed,
+                                 unsigned long long first_index) {
+  MG_ENSURE_INIT();
+  if (n == 0) return MG_OK;
+  if (!dst) return mg::fail(MG_ERR_INVALID, "mg_fill_uniform01: null pointer");
+  mg::uniform01_kernel<<<mg::grid_for(n, 256, 8), 256, 0, mg::ctx().stream>>>(dst, n, seed, first_index);
+  MG_LAUNCH_CHECK("uniform01");
   return MG_OK;
 }

@@ -21,6 +21,37 @@ def shard_rows(total_rows: int, rank: int, world: int) -> tuple[int, int]:
     return begin, begin + base + (1 if rank < extra else 0)
 
 
+def bind_near_gpu(device_index: int) -> dict:
+    """Restricts this process to the CPUs of the NUMA node its GPU hangs off, so that
+    pinned staging buffers allocated afterwards are local to that GPU's PCIe root
+    (eight ranks staging through one socket's memory share its bandwidth).  Uses
+    only what the process is already allowed to run on; returns what was done."""
+    info = {"numa_node": None, "bound": False, "cpus": len(os.sched_getaffinity(0))}
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        bus = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(device_index)).busId
+        bus = bus.decode() if isinstance(bus, bytes) else bus
+        # NVML prints an 8-digit PCI domain, sysfs a 4-digit one
+        dom, rest = bus.split(":", 1)
+        sysfs = f"/sys/bus/pci/devices/{dom[-4:].lower()}:{rest.lower()}"
+        with open(os.path.join(sysfs, "numa_node")) as f:
+            info["numa_node"] = int(f.read().strip())
+        with open(os.path.join(sysfs, "local_cpulist")) as f:
+            local = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                local.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0) & local
+        if allowed and allowed != os.sched_getaffinity(0):
+            os.sched_setaffinity(0, allowed)
+            info["bound"] = True
+        info["cpus"] = len(os.sched_getaffinity(0))
+    except Exception as exc:  # no NVML, no sysfs entry, or not permitted: stay as launched
+        info["note"] = f"{type(exc).__name__}: {exc}"[:120]
+    return info
+
+
 def env_rank_world() -> tuple[int, int, int]:
     return (int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")),
             int(os.environ.get("LOCAL_RANK", "0")))

@@ -320,7 +320,11 @@ void SGD::reduce_bucket(size_t bucket) {
     g.device_update();  // logical zeros become real zeros
     g.set_exchange_pending(true);
   }
-  check(mg_allreduce_sum_async(flat_grad_ + b.begin, b.end - b.begin), "gradient all-reduce");
+  // The bucket that completes the set has nothing left to hide behind: step() is
+  // about to wait for it, so it may use most of the GPU.
+  const bool last_one = buckets_.unreduced().size() == 1;
+  check(mg_allreduce_sum_async_hint(flat_grad_ + b.begin, b.end - b.begin, last_one ? 1 : 0),
+        "gradient all-reduce");
   buckets_.mark_reduced(bucket);
 }
 

@@ -108,7 +108,14 @@ def main():
         lin.weights().set_data(W)
         lin.bias().set_data(bias)
         layers.append(lin)
-    opt = api.SGD([t for lin in layers for t in (lin.weights(), lin.bias())], lr)
+    # A layer the graph never uses rides along in the optimiser: its bucket is never
+    # completed by a backward sweep, so step() has to exchange it itself (all ranks
+    # alike) instead of hanging or applying a rank-local gradient.
+    spare = api.Linear(16, 8)
+    spare_w = rng.standard_normal((16, 8))
+    spare.weights().set_data(spare_w)
+    opt = api.SGD([t for lin in layers for t in (lin.weights(), lin.bias())] +
+                  [spare.weights(), spare.bias()], lr)
     opt.enable_allreduce()
     x = api.Tensor([e - b, sizes[0]], X[b:e])
     x.set_requires_grad(False)
@@ -128,11 +135,34 @@ def main():
         losses.append(float(t.item()))
     ids = api.argmax_rows(logits_of(x))
     abi.mg_check_kernel_status()
+    ok_extra = np.array_equal(spare.weights().data(), spare_w.reshape(-1)) and not spare.bias().data().any()
+    if not ok_extra:
+        print(f"rank {rank}: the unused layer's parameters changed")
+    # A second backward() before step(): the first sweep's gradients are already summed
+    # over the ranks, so the library refuses instead of reducing them a second time.
+    final = [(lin.weights().data().copy(), lin.bias().data().copy()) for lin in layers]
+    loss = api.softmax_cross_entropy(logits_of(x), y[b:e], batch)
+    opt.zero_grad()
+    loss.backward()
+    try:
+        loss.backward()
+        refused = False
+    except RuntimeError as exc:
+        refused = "before step()" in str(exc)
+    if not refused:
+        ok_extra = False
+        print(f"rank {rank}: a second backward() before step() was not refused")
+    opt.zero_grad()                                       # drops the sweep; parameters untouched
+    abi.mg_sync()
+    for lin, (w0, b0) in zip(layers, final):
+        if not (np.array_equal(lin.weights().data(), w0) and np.array_equal(lin.bias().data(), b0)):
+            ok_extra = False
+            print(f"rank {rank}: parameters changed by the refused sweep")
 
     import oracle
     fast = oracle.fast
     ref = [(W.copy(), bias.copy()) for W, bias in params]
-    ok = allreduce_ok
+    ok = allreduce_ok and ok_extra
     for s in range(steps):
         ref_loss, _, _ = fast.mlp_train_step(ref, X, y, lr)
         if abs(losses[s] - ref_loss) > 1e-10 * abs(ref_loss):
