@@ -62,8 +62,10 @@ struct TileCfg {
   static constexpr int BM = WARPS_M * MT * 16, BN = WARPS_N * NT * 8;
   static constexpr int A_BYTES = BM * BK * 8, B_BYTES = BN * BK * 8;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  // full + empty barrier per stage, plus the consumers' meeting point around the tile ticket
+  static constexpr int kBarriers = 2 * STAGES + 1;
   static constexpr int SMEM_BYTES =
-      STAGES * STAGE_BYTES + 1024 /* alignment slack */ + (2 * STAGES + 1) * 8 /* barriers */;
+      STAGES * STAGE_BYTES + 1024 /* alignment slack */ + kBarriers * 8;
   // The ReLU-mask source tile of an output tile, staged through the same ring
   // after the last k-tile: BN/16 boxes of BM rows x 16 columns (128-byte rows).
   static constexpr int MASK_BOXES = BN / 16, MASK_BOX_BYTES = BM * 128;
@@ -309,7 +311,8 @@ dmma_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
                                               ~static_cast<uintptr_t>(1023));
   uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + kStages * kStageBytes);
   uint64_t *empty_bar = full_bar + kStages;
-  uint64_t *fold_bar = empty_bar + kStages;  // consumer warps meet here around the tile ticket
+  uint64_t *fold_bar = full_bar + 2 * kStages;  // consumer warps meet here around the tile ticket
+  static_assert(2 * kStages + 1 == Cfg::kBarriers, "barrier area and its users out of step");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int KT = (K + BK - 1) / BK;
@@ -773,7 +776,7 @@ static int launch_dmma_kernel(const DmmaLaunch &L) {
   // hardware scheduler's longest-first pairing, so they never run persistently.
   bool persistent = !L.table && (L.min_nkt < 32 || Cfg::BN <= 32) && L.items > ctx().sm_count;
   if (persist_mode == 0) persistent = false;
-  if (persist_mode == 1) persistent = true;
+  if (persist_mode == 1 && !L.table && L.items > ctx().sm_count) persistent = true;
   if (persistent) return launch_dmma_variant<AK, BK_, SHAPE, EDGE, Cfg, true>(L);
   return launch_dmma_variant<AK, BK_, SHAPE, EDGE, Cfg, false>(L);
 }

@@ -65,17 +65,21 @@ __device__ __forceinline__ void finish_partials(double partial, double *partials
 
 // ---------------------------------------------------------------------------
 // Full sum (src/ops/Reduction.cpp:17-21).  8 B of traffic per element.
-// 1024-thread CTAs, at most kSumCtas of them (two per SM on a 148-SM part, but a
-// fixed number: the association order must depend on n alone), four independent
-// 32-byte loads in flight per thread.  Measured on B200 against 256-thread CTAs x
-// 1184: 7.2 vs 6.9 TB/s at 2^28 elements, and a shorter fold of the partials.
+// 256-thread CTAs, at least four resident per SM, at most kSumCtas of them (three
+// per SM on a 148-SM part, but a fixed number: the association order must depend on
+// n alone), four independent 32-byte loads in flight per thread.  Chosen from a
+// sweep on B200 over CTA sizes 128-1024, 2-8 loads in flight and 148-1184 CTAs:
+// 25.1 us at 2^24 elements and 296 us at 2^28 (7.25 TB/s).  A CTA of 1024 threads
+// that needs 64 registers is alone on its SM, and its end-of-CTA fold then idles
+// the SM: 28 us at 2^24.
 // ---------------------------------------------------------------------------
-constexpr int kSumThreads = 1024;
-constexpr int kSumCtas = 296;
+constexpr int kSumThreads = 256;
+constexpr int kSumMinCtasPerSm = 4;
+constexpr int kSumCtas = 444;
 static_assert(kSumCtas <= kReducePartials, "partials buffer too small");
 
 template <int VEC>
-__global__ void __launch_bounds__(kSumThreads)
+__global__ void __launch_bounds__(kSumThreads, kSumMinCtasPerSm)
 sum_all_kernel(const double *__restrict__ x, size_t n, double *partials, unsigned int *ticket,
                double *out) {
   __shared__ double smem32[32];
