@@ -607,11 +607,28 @@ def small_batch_leg(abi, api):
     wall_ms = (time.perf_counter() - t0) * 1e3
     launches = (abi.mg_launch_count() - l0) / n
     flop = 454_400 * 32          # forward + weight gradients + hidden input gradients
+    # The same step recorded once (CUDA graph) and replayed with one launch per step.
+    del loss
+    rec = api.RecordedStep()
+    rec.begin()
+    loss = step()
+    rec.end()
+    for _ in range(20):
+        rec.replay()
+    abi.mg_sync()
+    t0 = time.perf_counter()
+    rec_ms = abi.timed_ms(lambda: [rec.replay() for _ in range(n)], 1)
+    rec_wall_ms = (time.perf_counter() - t0) * 1e3
+    float(loss.data()[0])
     return {"workload": "MLP 784-128-64-10 fp64 train step at batch 32 (benchmark config 1)",
             "us_per_step": dev_ms * 1e3 / n, "us_per_step_host_wall": wall_ms * 1e3 / n,
             "samples_per_s": 32 * n / (dev_ms * 1e-3), "launches_per_step": launches,
             "frac_of_nominal_fp64": flop / (dev_ms * 1e-3 / n) / 1e12 / NOMINAL_FP64_TFLOPS,
-            "bound": "kernel-launch latency (a chain of ~20 dependent micro-kernels)"}
+            "bound": "kernel-launch latency (a chain of ~20 dependent micro-kernels)",
+            "recorded_step": {"us_per_step": rec_ms * 1e3 / n, "us_per_step_host_wall": rec_wall_ms * 1e3 / n,
+                              "samples_per_s": 32 * n / (rec_ms * 1e-3), "kernels_per_replay": rec.kernels(),
+                              "what": "the same step recorded once with RecordedStep (a CUDA graph) and "
+                                      "replayed: one launch per step"}}
 
 
 def gemm_roofline(abi, K, rows):

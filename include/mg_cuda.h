@@ -223,6 +223,24 @@ int mg_sgd_step(double *param, const double *grad, double lr, size_t n); /* p -=
 int mg_sgd_step_multi(double *const *params, const double *const *grads, const size_t *sizes, int count,
                       double lr);
 
+/* ---- recorded steps (no counterpart in the reference) -------------------- */
+/* A launch-bound step — the reference trainer's batch-1 loop (src/main.cpp:20-46)
+ * is ~20 dependent micro-kernels per sample — can be recorded once and replayed
+ * with a single launch (a CUDA graph).  Between mg_graph_begin() and
+ * mg_graph_end() every kernel, fill, device copy, mg_alloc and mg_free on the
+ * compute stream is recorded instead of executed.  Entry points that wait for the
+ * device, use another stream or read host memory (mg_upload*, mg_download*,
+ * mg_sync, mg_check_kernel_status, the mg_comm_* exchange) fail with
+ * MG_ERR_INVALID while recording.  Run the step once normally first: GEMM segment
+ * tables and scratch buffers are created on first use and cannot be created while
+ * recording.  Buffers allocated while recording keep their addresses across
+ * replays, so results can be read (mg_download) after every mg_graph_launch(). */
+int mg_graph_begin(void);
+int mg_graph_end(int *out_id);
+int mg_graph_launch(int id);  /* enqueues the whole recorded step on the compute stream */
+int mg_graph_kernels(int id); /* kernel launches the recorded step contains (0 if unknown id) */
+int mg_graph_destroy(int id);
+
 /* ---- events / timing on the compute stream ------------------------------ */
 int mg_event_create(int *out_id);
 int mg_event_record(int id);

@@ -107,6 +107,12 @@ int mgt_comm_unique_id(char *out128);
 int mgt_comm_init(const char *id128, int rank, int world);
 int mgt_comm_shutdown(void);
 int mgt_sgd_enable_allreduce(mgt_sgd s);
+/* Tensor::copy_from_host and micrograd::RecordedStep (one recorded step per process here). */
+int mgt_copy_from_host(mgt_tensor t, const double *values, size_t n);
+int mgt_record_begin(void);
+int mgt_record_end(void);
+int mgt_record_replay(void);
+int mgt_record_kernels(void);
 #endif
 
 #ifdef __cplusplus

@@ -18,6 +18,38 @@ enum class Backend { CPU, Metal, CUDA };
 // Blocks until all device work enqueued so far has finished.
 void synchronize();
 
+// A launch-bound step — the reference trainer's per-sample loop
+// (src/main.cpp:20-46) enqueues about twenty dependent micro-kernels per sample —
+// recorded once and replayed with a single launch (a CUDA graph):
+//
+//   x->copy_from_host(first_batch);  step();          // run it once normally
+//   RecordedStep rec;  rec.begin();  loss = step();  rec.end();
+//   for (...) { x->copy_from_host(next_batch);  rec.replay();  loss->at({0}); }
+//
+// step() is ordinary code on the Tensor API (forward, loss, zero_grad, backward,
+// SGD::step).  Rules while recording: no host reads (data(), grad(), at(),
+// argmax_rows) and no tensors built from host values; labels are passed as a
+// Tensor; every tensor that exists before begin() must outlive end().  Inputs are
+// tensors created before begin() and refreshed with copy_from_host(); tensors
+// created while recording that are still referenced afterwards (the loss) keep
+// their device address, and reading them after replay() returns that replay's
+// values.  Parameters are updated in place by every replay.
+class RecordedStep {
+public:
+  RecordedStep() = default;
+  ~RecordedStep();
+  RecordedStep(const RecordedStep &) = delete;
+  RecordedStep &operator=(const RecordedStep &) = delete;
+  void begin();
+  void end();
+  void replay();
+  bool recorded() const { return id_ >= 0; }
+  int kernels() const;  // kernel launches one replay stands for
+
+private:
+  int id_ = -1;
+};
+
 // Data-parallel training, one process per GPU.  Rank 0 obtains an id with
 // comm_unique_id(), ships the 128 bytes to the other ranks by any host channel,
 // and every rank calls comm_init().  After SGD::enable_allreduce(), backward()

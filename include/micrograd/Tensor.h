@@ -81,6 +81,10 @@ public:
   // Uploads straight from caller memory (pinned or pageable) without the
   // intermediate std::vector the reference constructor takes by value.
   static std::shared_ptr<Tensor> from_host(std::vector<size_t> shape, const double *values);
+  // Overwrites the values with size() doubles from caller memory, keeping the
+  // device buffer (and its address) the tensor already has: how the input of a
+  // recorded step is refreshed.
+  void copy_from_host(const double *values);
   // Read-only host views.  Unlike the mutable data()/grad() of the reference
   // interface they do not hand out a writable reference, so the device copy stays
   // current and no re-upload follows the read.

@@ -56,6 +56,11 @@ public:
   // enqueued after the producer.  No effect on larger buffers.
   void mirror_async();
 
+  // Overwrites the contents with `size()` values from caller memory, in the device
+  // buffer this storage already has (its address does not change, which a recorded
+  // step relies on).
+  void upload_in_place(const double *values);
+
   // Moves the contents into caller-owned device memory (a slice of a flat
   // parameter/gradient buffer) and uses that memory from now on.
   // `keepalive` owns that memory.
@@ -89,6 +94,7 @@ private:
   bool dev_valid_ = false;   // dev_ holds the current values
   bool host_valid_ = false;  // host_ holds the current values
   unsigned long long write_stamp_ = 0;
+  unsigned long long host_epoch_ = 0;  // device epoch at which host_ was last made current
   bool comm_pending_ = false;  // an all-reduce on the communication stream targets dev_
   int pending_upload_ = -1;  // event id of a prefetch the compute stream has not waited for
   unsigned long long mirror_ticket_ = 0;  // pending scalar mirror (0: none)
@@ -111,6 +117,12 @@ private:
   int *dev_ = nullptr;
   size_t n_ = 0;
 };
+
+// Counts replays of recorded steps.  A replay rewrites device buffers without
+// passing through the host-side bookkeeping, so a host copy taken in an earlier
+// epoch is stale whenever the device buffer is the authority.
+unsigned long long device_epoch();
+void advance_device_epoch();
 
 // Throws std::runtime_error carrying mg_last_error() when rc != 0.
 void check(int rc, const char *what);

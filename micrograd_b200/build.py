@@ -154,7 +154,7 @@ def build_cpp_tests(force: bool = False, verbose: bool = False, reference: str |
     out = os.path.join(bindir, "trainer_loop")
     src = os.path.join(tests, "trainer_loop.cpp")
     if force or _newer(out, [src, lib]):
-        _run(common + [src, "-o", out] + link + rpath, verbose)
+        _run(common + ["-DMG_TRAINER_RECORDED", src, "-o", out] + link + rpath, verbose)
     built.append(out)
     reference = reference or reference_dir()
     ref_test = os.path.join(reference, "test", "tensor_test.cpp")

@@ -79,6 +79,11 @@ SIGNATURES = {
     "mg_f64_to_i32": (C.c_int, [C.c_void_p, C.c_void_p, _sz]),
     "mg_avg_pool_28": (C.c_int, [C.c_void_p, C.c_void_p, _sz]),
     "mg_sgd_step": (C.c_int, [C.c_void_p, C.c_void_p, C.c_double, _sz]),
+    "mg_graph_begin": (C.c_int, []),
+    "mg_graph_end": (C.c_int, [_ip]),
+    "mg_graph_launch": (C.c_int, [C.c_int]),
+    "mg_graph_kernels": (C.c_int, [C.c_int]),
+    "mg_graph_destroy": (C.c_int, [C.c_int]),
     "mg_event_create": (C.c_int, [_ip]),
     "mg_event_record": (C.c_int, [C.c_int]),
     "mg_event_elapsed_ms": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_float)]),
@@ -111,7 +116,8 @@ SIGNATURES = {
 }
 
 # Entry points whose int result is a value, not a status.
-_VALUE_INT = {"mg_device", "mg_sm_count", "mg_comm_rank", "mg_comm_world", "mg_comm_peer_path"}
+_VALUE_INT = {"mg_device", "mg_sm_count", "mg_comm_rank", "mg_comm_world", "mg_comm_peer_path",
+              "mg_graph_kernels"}
 
 
 def declared_in_header(header_text: str) -> list[str]:

@@ -396,6 +396,7 @@ int mg_allreduce_sum_async(double *buf, size_t n) { return mg_allreduce_sum_asyn
 
 int mg_allreduce_sum_async_hint(double *buf, size_t n, int exposed) {
   MG_ENSURE_INIT();
+  MG_NOT_WHILE_RECORDING("mg_allreduce_sum_async");
   if (n == 0) return MG_OK;
   if (!buf) return fail(MG_ERR_INVALID, "mg_allreduce_sum_async: null buffer");
   if (!g_comm) {
@@ -549,6 +550,7 @@ int mg_comm_peer_path(const double *ptr) {
 
 int mg_comm_join(void) {
   MG_ENSURE_INIT();
+  MG_NOT_WHILE_RECORDING("mg_comm_join");
   Context &c = ctx();
   cudaEvent_t t0 = nullptr, t1 = nullptr;
   if (g_trace.on && (t0 = trace_event()) && (t1 = trace_event()))

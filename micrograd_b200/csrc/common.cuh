@@ -44,6 +44,9 @@ struct Context {
   void *flush_buf = nullptr;
   size_t flush_bytes = 0;
   unsigned long long launches = 0;
+  // True between mg_graph_begin() and mg_graph_end(): everything enqueued on the
+  // compute stream is being recorded into a CUDA graph instead of executed.
+  bool capturing = false;
 };
 
 Context &ctx();
@@ -73,6 +76,15 @@ inline void count_launch() { ctx().launches++; }
   do {                                                                                             \
     int mg_rc_ = ::mg::ensure_init();                                                              \
     if (mg_rc_ != MG_OK) return mg_rc_;                                                            \
+  } while (0)
+
+// Entry points that wait for the device, touch other streams or read host memory
+// later cannot be part of a recorded step.
+#define MG_NOT_WHILE_RECORDING(name)                                                               \
+  do {                                                                                             \
+    if (::mg::ctx().capturing)                                                                     \
+      return ::mg::fail(MG_ERR_INVALID, name ": not allowed while a step is being recorded "       \
+                                             "(between mg_graph_begin and mg_graph_end)");         \
   } while (0)
 
 #define MG_LAUNCH_CHECK(name)                                                                      \

@@ -16,6 +16,11 @@ thread_local std::string t_last_error;
 std::mutex g_init_mutex;
 Context g_ctx;
 std::vector<cudaEvent_t> g_events;
+struct RecordedStep {
+  cudaGraphExec_t exec = nullptr;
+  unsigned long long kernels = 0;  // kernel nodes, for the launch counter
+};
+std::vector<RecordedStep> g_steps;
 }  // namespace
 
 Context &ctx() { return g_ctx; }
@@ -103,6 +108,10 @@ int ensure_init() {
 int ensure_scratch(double **buf, size_t *have, size_t elems) {
   if (*have >= elems) return MG_OK;
   Context &c = ctx();
+  if (c.capturing)
+    return fail(MG_ERR_INVALID,
+                "a scratch buffer would have to grow while a step is being recorded; run the step "
+                "once before mg_graph_begin()");
   if (*buf) MG_CUDA_TRY(cudaFreeAsync(*buf, c.stream));
   *buf = nullptr;
   *have = 0;
@@ -150,6 +159,9 @@ int mg_shutdown(void) {
   for (cudaEvent_t ev : g_events)
     if (ev) cudaEventDestroy(ev);
   g_events.clear();
+  for (auto &step : g_steps)
+    if (step.exec) cudaGraphExecDestroy(step.exec);
+  g_steps.clear();
   release_mirror_ring_at_shutdown();
   if (c.colsum_scratch) cudaFreeAsync(c.colsum_scratch, c.stream);
   if (c.splitk_scratch) cudaFreeAsync(c.splitk_scratch, c.stream);
@@ -183,6 +195,7 @@ static cudaStream_t g_mirror_stream_for_sync();
 
 int mg_sync(void) {
   MG_ENSURE_INIT();
+  MG_NOT_WHILE_RECORDING("mg_sync");
   MG_CUDA_TRY(cudaStreamSynchronize(g_ctx.stream));
   MG_CUDA_TRY(cudaStreamSynchronize(g_ctx.comm_stream));
   MG_CUDA_TRY(cudaStreamSynchronize(g_ctx.copy_stream));
@@ -192,6 +205,7 @@ int mg_sync(void) {
 
 int mg_check_kernel_status(void) {
   MG_ENSURE_INIT();
+  MG_NOT_WHILE_RECORDING("mg_check_kernel_status");
   int status = 0;
   MG_CUDA_TRY(cudaMemcpyAsync(&status, g_ctx.kernel_status, sizeof(int), cudaMemcpyDeviceToHost,
                               g_ctx.stream));
@@ -208,6 +222,7 @@ int mg_check_kernel_status(void) {
 
 int mg_kernel_status_mirror(void) {
   MG_ENSURE_INIT();
+  MG_NOT_WHILE_RECORDING("mg_kernel_status_mirror");
   Context &c = g_ctx;
   if (!c.status_host) {
     MG_CUDA_TRY(cudaMallocHost(&c.status_host, sizeof(int)));
@@ -262,6 +277,7 @@ int mg_free_i32(int *p) { return mg_free(reinterpret_cast<double *>(p)); }
 
 int mg_upload(double *dst, const double *src_host, size_t n) {
   MG_ENSURE_INIT();
+  MG_NOT_WHILE_RECORDING("mg_upload (the host address would be baked into the graph)");
   if (n == 0) return MG_OK;
   if (!dst || !src_host) return fail(MG_ERR_INVALID, "mg_upload: null pointer");
   MG_CUDA_TRY(cudaMemcpyAsync(dst, src_host, n * sizeof(double), cudaMemcpyHostToDevice,
@@ -271,6 +287,7 @@ int mg_upload(double *dst, const double *src_host, size_t n) {
 
 int mg_upload_async(double *dst, const double *src_host, size_t n, int *out_event_id) {
   MG_ENSURE_INIT();
+  MG_NOT_WHILE_RECORDING("mg_upload_async");
   if (!out_event_id) return fail(MG_ERR_INVALID, "mg_upload_async: null event pointer");
   if (n && (!dst || !src_host)) return fail(MG_ERR_INVALID, "mg_upload_async: null pointer");
   Context &c = g_ctx;
@@ -300,6 +317,7 @@ int mg_compute_wait_event(int id) {
 
 int mg_download(double *dst_host, const double *src, size_t n) {
   MG_ENSURE_INIT();
+  MG_NOT_WHILE_RECORDING("mg_download");
   if (n == 0) return MG_OK;
   if (!dst_host || !src) return fail(MG_ERR_INVALID, "mg_download: null pointer");
   MG_CUDA_TRY(cudaMemcpyAsync(dst_host, src, n * sizeof(double), cudaMemcpyDeviceToHost,
@@ -310,6 +328,7 @@ int mg_download(double *dst_host, const double *src, size_t n) {
 
 int mg_upload_i32(int *dst, const int *src_host, size_t n) {
   MG_ENSURE_INIT();
+  MG_NOT_WHILE_RECORDING("mg_upload_i32 (the host address would be baked into the graph)");
   if (n == 0) return MG_OK;
   if (!dst || !src_host) return fail(MG_ERR_INVALID, "mg_upload_i32: null pointer");
   MG_CUDA_TRY(cudaMemcpyAsync(dst, src_host, n * sizeof(int), cudaMemcpyHostToDevice,
@@ -319,6 +338,7 @@ int mg_upload_i32(int *dst, const int *src_host, size_t n) {
 
 int mg_download_i32(int *dst_host, const int *src, size_t n) {
   MG_ENSURE_INIT();
+  MG_NOT_WHILE_RECORDING("mg_download_i32");
   if (n == 0) return MG_OK;
   if (!dst_host || !src) return fail(MG_ERR_INVALID, "mg_download_i32: null pointer");
   MG_CUDA_TRY(cudaMemcpyAsync(dst_host, src, n * sizeof(int), cudaMemcpyDeviceToHost,
@@ -380,6 +400,12 @@ static cudaStream_t g_mirror_stream_for_sync() { return g_mirror.stream; }
 int mg_scalar_mirror(const double *src, unsigned long long *out_ticket) {
   MG_ENSURE_INIT();
   if (!src || !out_ticket) return fail(MG_ERR_INVALID, "mg_scalar_mirror: null pointer");
+  if (g_ctx.capturing) {
+    // A mirror runs on a stream of its own; a recorded step stays on one stream.
+    // Ticket 0 is never valid, so a later fetch falls back to an ordinary download.
+    *out_ticket = 0;
+    return MG_OK;
+  }
   int rc = mirror_ring_init();
   if (rc != MG_OK) return rc;
   MirrorRing &m = g_mirror;
@@ -419,6 +445,93 @@ int mg_host_alloc(size_t bytes, void **out_host) {
 int mg_host_free(void *host) {
   if (!host) return MG_OK;
   MG_CUDA_TRY(cudaFreeHost(host));
+  return MG_OK;
+}
+
+/* ---- recorded steps (CUDA graphs) ---- */
+// A launch-bound step (a batch-1 or batch-32 training step is ~20 dependent
+// micro-kernels) costs mostly launch overhead.  Between mg_graph_begin() and
+// mg_graph_end() everything the library enqueues on its compute stream —
+// kernels, fills, device copies, pool allocations and frees — is recorded instead
+// of executed; mg_graph_launch() then replays the whole step with one launch.
+// Buffers allocated while recording keep their addresses across replays (the
+// graph owns them and re-creates them at every launch), so a tensor produced by
+// the recorded step can be read after each replay.
+int mg_graph_begin(void) {
+  MG_ENSURE_INIT();
+  Context &c = g_ctx;
+  if (c.capturing) return fail(MG_ERR_INVALID, "mg_graph_begin: a step is already being recorded");
+  MG_CUDA_TRY(cudaStreamSynchronize(c.stream));
+  MG_CUDA_TRY(cudaStreamBeginCapture(c.stream, cudaStreamCaptureModeRelaxed));
+  c.capturing = true;
+  return MG_OK;
+}
+
+int mg_graph_end(int *out_id) {
+  MG_ENSURE_INIT();
+  Context &c = g_ctx;
+  if (!c.capturing) return fail(MG_ERR_INVALID, "mg_graph_end: no step is being recorded");
+  c.capturing = false;
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture(c.stream, &graph);
+  if (e != cudaSuccess || !graph) {
+    cudaGetLastError();
+    return fail(MG_ERR_CUDA, "recording the step failed: %s", cudaGetErrorString(e));
+  }
+  if (!out_id) {
+    cudaGraphDestroy(graph);
+    return fail(MG_ERR_INVALID, "mg_graph_end: null out pointer");
+  }
+  RecordedStep step;
+  size_t count = 0;
+  if (cudaGraphGetNodes(graph, nullptr, &count) == cudaSuccess && count > 0) {
+    std::vector<cudaGraphNode_t> nodes(count);
+    if (cudaGraphGetNodes(graph, nodes.data(), &count) == cudaSuccess) {
+      for (size_t i = 0; i < count; i++) {
+        cudaGraphNodeType type;
+        if (cudaGraphNodeGetType(nodes[i], &type) == cudaSuccess && type == cudaGraphNodeTypeKernel)
+          step.kernels++;
+      }
+    }
+  }
+  // Allocations made while recording and still live are released and re-made by
+  // every launch, at the same addresses.
+  e = cudaGraphInstantiateWithFlags(&step.exec, graph, cudaGraphInstantiateFlagAutoFreeOnLaunch);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGraphInstantiate");
+  for (size_t i = 0; i < g_steps.size(); i++) {
+    if (!g_steps[i].exec) {
+      g_steps[i] = step;
+      *out_id = (int)i;
+      return MG_OK;
+    }
+  }
+  g_steps.push_back(step);
+  *out_id = (int)g_steps.size() - 1;
+  return MG_OK;
+}
+
+int mg_graph_launch(int id) {
+  MG_ENSURE_INIT();
+  MG_NOT_WHILE_RECORDING("mg_graph_launch");
+  if (id < 0 || (size_t)id >= g_steps.size() || !g_steps[id].exec)
+    return fail(MG_ERR_INVALID, "unknown recorded step %d", id);
+  MG_CUDA_TRY(cudaGraphLaunch(g_steps[id].exec, g_ctx.stream));
+  g_ctx.launches += g_steps[id].kernels;
+  return MG_OK;
+}
+
+int mg_graph_kernels(int id) {
+  if (id < 0 || (size_t)id >= g_steps.size() || !g_steps[id].exec) return 0;
+  return (int)g_steps[id].kernels;
+}
+
+int mg_graph_destroy(int id) {
+  if (id < 0 || (size_t)id >= g_steps.size() || !g_steps[id].exec)
+    return fail(MG_ERR_INVALID, "unknown recorded step %d", id);
+  if (g_ctx.ready) cudaStreamSynchronize(g_ctx.stream);
+  cudaGraphExecDestroy(g_steps[id].exec);
+  g_steps[id] = RecordedStep();
   return MG_OK;
 }
 

@@ -738,6 +738,7 @@ int mg_avg_pool_28(const double *x, double *out, size_t batch) {
 
 int mg_upload_u8_scaled(double *dst, const unsigned char *src_host, size_t n, double divisor) {
   MG_ENSURE_INIT();
+  MG_NOT_WHILE_RECORDING("mg_upload_u8_scaled");
   if (n == 0) return MG_OK;
   if (!dst || !src_host) return fail(MG_ERR_INVALID, "mg_upload_u8_scaled: null pointer");
   if (divisor == 0.0) return fail(MG_ERR_INVALID, "mg_upload_u8_scaled: divisor is zero");

@@ -987,6 +987,10 @@ static int seg_table_for(int tiles_m, int tiles_n, int KT, int bm, int bn, int s
       return MG_OK;
     }
   }
+  if (ctx().capturing)
+    return fail(MG_ERR_INVALID,
+                "a GEMM of a new shape needs its segment table built while a step is being recorded; "
+                "run the step once before mg_graph_begin()");
   // A job with ever-changing shapes (e.g. a varying batch) would grow the cache
   // without bound: start over beyond 256 tables (cudaFree waits for the kernels
   // that still read them).

@@ -9,6 +9,30 @@ using detail::check;
 
 void synchronize() { check(mg_sync(), "synchronize"); }
 
+RecordedStep::~RecordedStep() {
+  if (id_ >= 0) {
+    mg_graph_destroy(id_);
+  }
+}
+
+void RecordedStep::begin() {
+  if (id_ >= 0) {
+    check(mg_graph_destroy(id_), "recorded step");
+    id_ = -1;
+  }
+  check(mg_graph_begin(), "begin recording");
+}
+
+void RecordedStep::end() { check(mg_graph_end(&id_), "end recording"); }
+
+void RecordedStep::replay() {
+  check(mg_graph_launch(id_), "replay");
+  // Whatever the step wrote on the device is newer than any host copy.
+  detail::advance_device_epoch();
+}
+
+int RecordedStep::kernels() const { return mg_graph_kernels(id_); }
+
 void comm_unique_id(char *out128) { check(mg_comm_unique_id(out128), "comm_unique_id"); }
 
 void comm_init(const char *id128, int rank, int world) {

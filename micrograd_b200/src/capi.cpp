@@ -402,6 +402,33 @@ int mgt_sgd_enable_allreduce(mgt_sgd s) {
   return guard_int([&] { s->s.enable_allreduce(); });
 }
 
+int mgt_copy_from_host(mgt_tensor t, const double *values, size_t n) {
+  return guard_int([&] {
+    if (n != t->p->size()) {
+      throw std::invalid_argument("mgt_copy_from_host: size mismatch");
+    }
+    t->p->copy_from_host(values);
+  });
+}
+
+namespace {
+micrograd::RecordedStep g_recorded_step;
+}
+
+int mgt_record_begin(void) {
+  return guard_int([&] { g_recorded_step.begin(); });
+}
+
+int mgt_record_end(void) {
+  return guard_int([&] { g_recorded_step.end(); });
+}
+
+int mgt_record_replay(void) {
+  return guard_int([&] { g_recorded_step.replay(); });
+}
+
+int mgt_record_kernels(void) { return g_recorded_step.kernels(); }
+
 #endif // MG_B200_EXTENSIONS
 
 } // extern "C"

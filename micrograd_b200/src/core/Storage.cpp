@@ -10,7 +10,11 @@ namespace micrograd::detail {
 
 namespace {
 constexpr size_t kKeepHostElems = 4096;
+unsigned long long g_device_epoch = 0;
 }
+
+unsigned long long device_epoch() { return g_device_epoch; }
+void advance_device_epoch() { g_device_epoch++; }
 
 void check(int rc, const char *what) {
   if (rc != MG_OK) {
@@ -62,6 +66,7 @@ void Storage::init_from_host(std::vector<double> &&values) {
   if (size_ <= kKeepHostElems) {
     host_ = std::move(values);
     host_valid_ = true;
+    host_epoch_ = g_device_epoch;
   } else {
     host_valid_ = false;
   }
@@ -109,6 +114,7 @@ void Storage::sync_host_from_device() {
     check(mg_download(host_.data(), dev_, size_), "download");
   }
   host_valid_ = true;
+  host_epoch_ = g_device_epoch;
 }
 
 // A one-element result is copied to pinned host memory right behind its producer,
@@ -218,7 +224,8 @@ const std::vector<double> &Storage::host_const() {
     // A read does not end the logical-zero state: the next accumulation is still
     // a plain store and no buffer has to be filled.
     host_.assign(size_, 0.0);
-  } else if (!host_valid_) {
+  } else if (!host_valid_ || (dev_valid_ && host_epoch_ != g_device_epoch)) {
+    // (second case: a recorded step was replayed since the host copy was taken)
     sync_host_from_device();
   }
   return host_;
@@ -229,7 +236,7 @@ double Storage::peek(size_t index) {
   if (zero_ || index >= size_) {
     return 0.0;
   }
-  if (host_valid_) {
+  if (host_valid_ && !(dev_valid_ && host_epoch_ != g_device_epoch)) {
     return host_[index];
   }
   double v = 0.0;
@@ -239,6 +246,16 @@ double Storage::peek(size_t index) {
   settle_exchange();
   check(mg_download(&v, dev_ + index, 1), "download");
   return v;
+}
+
+void Storage::upload_in_place(const double *values) {
+  write_stamp_++;
+  settle_upload();
+  ensure_device_buffer();
+  check(mg_upload(dev_, values, size_), "upload");
+  zero_ = false;
+  dev_valid_ = true;
+  host_valid_ = false;
 }
 
 void Storage::rehome(double *slice, std::shared_ptr<void> keepalive) {

@@ -89,6 +89,11 @@ def _declare(lib, extensions: bool) -> None:
             "mgt_comm_init": (C.c_int, [C.c_char_p, C.c_int, C.c_int]),
             "mgt_comm_shutdown": (C.c_int, []),
             "mgt_sgd_enable_allreduce": (C.c_int, [vp]),
+            "mgt_copy_from_host": (C.c_int, [vp, _c_double_p, C.c_size_t]),
+            "mgt_record_begin": (C.c_int, []),
+            "mgt_record_end": (C.c_int, []),
+            "mgt_record_replay": (C.c_int, []),
+            "mgt_record_kernels": (C.c_int, []),
         })
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)
@@ -233,6 +238,11 @@ def bind(path: str) -> SimpleNamespace:
         def set_requires_grad(self, flag: bool) -> None:
             _check(lib.mgt_set_requires_grad(self._h, 1 if flag else 0))
 
+        def copy_from_host(self, values) -> None:
+            """Tensor::copy_from_host: new values into the device buffer the tensor has."""
+            arr = _as_f64(values)
+            _check(lib.mgt_copy_from_host(self._h, arr.ctypes.data_as(_c_double_p), arr.size))
+
     class Linear:
         """Mirror of ``class Linear`` (reference include/micrograd/nn.h:10-21)."""
 
@@ -320,6 +330,15 @@ def bind(path: str) -> SimpleNamespace:
 
     def comm_shutdown() -> None: _check(lib.mgt_comm_shutdown())
 
+    class RecordedStep:
+        """micrograd::RecordedStep — record one step of Tensor-API code, replay it
+        with a single launch (one recorded step per process through this binding)."""
+
+        def begin(self) -> None: _check(lib.mgt_record_begin())
+        def end(self) -> None: _check(lib.mgt_record_end())
+        def replay(self) -> None: _check(lib.mgt_record_replay())
+        def kernels(self) -> int: return int(lib.mgt_record_kernels())
+
     return SimpleNamespace(
         lib=lib, extensions=extensions, Tensor=Tensor, Linear=Linear, SGD=SGD,
         mse_loss=mse_loss, avg_pool_2x2=avg_pool_2x2, save_model=save_model,
@@ -327,5 +346,5 @@ def bind(path: str) -> SimpleNamespace:
         softmax_cross_entropy=softmax_cross_entropy, argmax_rows=argmax_rows, from_host=from_host,
         comm_rank=lambda: int(lib.mgt_comm_rank()), comm_world=lambda: int(lib.mgt_comm_world()),
         synchronize=synchronize, comm_unique_id=comm_unique_id, comm_init=comm_init,
-        comm_shutdown=comm_shutdown,
+        comm_shutdown=comm_shutdown, RecordedStep=RecordedStep if extensions else None,
     )
