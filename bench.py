@@ -879,11 +879,18 @@ def main():
                     help="diagnostic: host waits for the device after every step")
     ap.add_argument("--sweeps-only", action="store_true",
                     help="run only the DGEMM / elementwise sweeps on one GPU (for profiler captures)")
+    ap.add_argument("--small-only", action="store_true",
+                    help="run only the batch-32 step of config 1 on one GPU (for profiler captures)")
     ap.add_argument("--value-only", action="store_true",
                     help="run only the device-resident leg (for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.small_only:
+        import micrograd_b200
+        abi = micrograd_b200.load_abi()
+        abi.mg_init(0)
+        print(json.dumps({"c1": small_batch_leg(abi, micrograd_b200.load_api())}), flush=True)
     elif args.sweeps_only:
         import micrograd_b200
         from micrograd_b200 import cabi as K
