@@ -113,6 +113,7 @@ int mgt_record_begin(void);
 int mgt_record_end(void);
 int mgt_record_replay(void);
 int mgt_record_kernels(void);
+int mgt_record_abandon(void); /* what ~RecordedStep does to a recording that was never ended */
 #endif
 
 #ifdef __cplusplus

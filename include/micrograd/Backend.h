@@ -48,6 +48,7 @@ public:
 
 private:
   int id_ = -1;
+  bool recording_ = false;
 };
 
 // Data-parallel training, one process per GPU.  Rank 0 obtains an id with

@@ -269,7 +269,14 @@ int mg_alloc_i32(size_t n, int **out) { return alloc_bytes(n * sizeof(int), (voi
 int mg_free(double *p) {
   if (!p) return MG_OK;
   if (!g_ctx.ready) return MG_OK;  // after shutdown the pool is gone with the context
-  MG_CUDA_TRY(cudaFreeAsync(p, g_ctx.stream));
+  cudaError_t e = cudaFreeAsync(p, g_ctx.stream);
+  if (e != cudaSuccess) {
+    // (e.g. a buffer of a recorded step that was never replayed: its address was only
+    // ever reserved.)  Clear the runtime's error slot so the next launch check does
+    // not report this failure as its own.
+    cudaGetLastError();
+    return cuda_fail(e, "cudaFreeAsync");
+  }
   return MG_OK;
 }
 

@@ -10,6 +10,14 @@ using detail::check;
 void synchronize() { check(mg_sync(), "synchronize"); }
 
 RecordedStep::~RecordedStep() {
+  if (recording_) {
+    // Abandoned between begin() and end(): close the recording so that later work
+    // executes again, and drop what was recorded.
+    int discarded = -1;
+    if (mg_graph_end(&discarded) == MG_OK && discarded >= 0) {
+      mg_graph_destroy(discarded);
+    }
+  }
   if (id_ >= 0) {
     mg_graph_destroy(id_);
   }
@@ -21,9 +29,13 @@ void RecordedStep::begin() {
     id_ = -1;
   }
   check(mg_graph_begin(), "begin recording");
+  recording_ = true;
 }
 
-void RecordedStep::end() { check(mg_graph_end(&id_), "end recording"); }
+void RecordedStep::end() {
+  recording_ = false;
+  check(mg_graph_end(&id_), "end recording");
+}
 
 void RecordedStep::replay() {
   check(mg_graph_launch(id_), "replay");

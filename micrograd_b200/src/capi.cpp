@@ -412,22 +412,28 @@ int mgt_copy_from_host(mgt_tensor t, const double *values, size_t n) {
 }
 
 namespace {
-micrograd::RecordedStep g_recorded_step;
+// The one recorded step this flat binding offers; replaced by a fresh object when
+// the caller abandons it.
+std::unique_ptr<micrograd::RecordedStep> g_recorded_step = std::make_unique<micrograd::RecordedStep>();
+}
+
+int mgt_record_abandon(void) {
+  return guard_int([&] { g_recorded_step = std::make_unique<micrograd::RecordedStep>(); });
 }
 
 int mgt_record_begin(void) {
-  return guard_int([&] { g_recorded_step.begin(); });
+  return guard_int([&] { g_recorded_step->begin(); });
 }
 
 int mgt_record_end(void) {
-  return guard_int([&] { g_recorded_step.end(); });
+  return guard_int([&] { g_recorded_step->end(); });
 }
 
 int mgt_record_replay(void) {
-  return guard_int([&] { g_recorded_step.replay(); });
+  return guard_int([&] { g_recorded_step->replay(); });
 }
 
-int mgt_record_kernels(void) { return g_recorded_step.kernels(); }
+int mgt_record_kernels(void) { return g_recorded_step->kernels(); }
 
 #endif // MG_B200_EXTENSIONS
 

@@ -94,6 +94,7 @@ def _declare(lib, extensions: bool) -> None:
             "mgt_record_end": (C.c_int, []),
             "mgt_record_replay": (C.c_int, []),
             "mgt_record_kernels": (C.c_int, []),
+            "mgt_record_abandon": (C.c_int, []),
         })
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)
@@ -338,6 +339,10 @@ def bind(path: str) -> SimpleNamespace:
         def end(self) -> None: _check(lib.mgt_record_end())
         def replay(self) -> None: _check(lib.mgt_record_replay())
         def kernels(self) -> int: return int(lib.mgt_record_kernels())
+
+        def abandon(self) -> None:
+            """Destroys the C++ object (as going out of scope would) and makes a new one."""
+            _check(lib.mgt_record_abandon())
 
     return SimpleNamespace(
         lib=lib, extensions=extensions, Tensor=Tensor, Linear=Linear, SGD=SGD,

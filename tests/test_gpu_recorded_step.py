@@ -136,3 +136,19 @@ def test_recorded_per_sample_trainer_step(api, abi, fast):
     abi.mg_check_kernel_status()
     assert rec_losses == eager_losses
     assert np.array_equal(rec_w, eager_w)
+
+
+def test_abandoned_recording_is_closed(api, abi):
+    """A RecordedStep dropped between begin() and end() ends the recording: work
+    enqueued afterwards executes again."""
+    rec = api.RecordedStep()
+    a = api.Tensor([4], [1.0, 2.0, 3.0, 4.0])
+    warm = a.mul(2.0).sum()
+    assert warm.data()[0] == 20.0
+    del warm
+    rec.begin()
+    pending = a.mul(3.0).sum()                 # recorded only
+    rec.abandon()
+    del pending
+    assert a.mul(3.0).sum().data()[0] == 30.0  # executes
+    abi.mg_check_kernel_status()
