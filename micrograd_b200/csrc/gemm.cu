@@ -1046,7 +1046,16 @@ static int run_gemm(const GemmDesc &d) {
 
   bool use_dmma = dmma_eligible(d) && d.K > 0;
   if (g_gemm_path == 1) use_dmma = false;
-  if (g_gemm_path == 0 && use_dmma && d.M * d.N * d.K < (size_t)64 * 64 * 64) use_dmma = false;
+  // Below M.N.K = 512 the plain kernel is used.  The bar used to be 64^3; measured on
+  // the launch-bound steps (batch-32 training step: 112.6 -> 97.3 us, recorded 83.9 ->
+  // 69.6 us; the per-sample trainer loop: 5.6 k -> 7.6 k samples/s), one CTA of the
+  // tensor-core kernel finishes a tiny product in less time than the plain
+  // kernel's chain of dependent 16-deep global loads.
+  static const size_t min_dmma_volume = [] {
+    const char *v = std::getenv("MG_GEMM_MIN_VOLUME");  // diagnostic
+    return v && *v ? (size_t)std::atoll(v) : (size_t)512;
+  }();
+  if (g_gemm_path == 0 && use_dmma && d.M * d.N * d.K < min_dmma_volume) use_dmma = false;
 
   const int M = (int)d.M, N = (int)d.N, K = (int)d.K;
   if (!use_dmma) {

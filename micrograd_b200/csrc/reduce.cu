@@ -190,7 +190,8 @@ sum_lastaxis_kernel(const double *__restrict__ x, double *__restrict__ out, size
 template <int VEC, int TX>
 __global__ void __launch_bounds__(256)
 colsum_partial_kernel(const double *__restrict__ g, double *__restrict__ gx, bool gx_accumulate,
-                      double *__restrict__ partials, size_t M, size_t N, size_t rows_per_chunk) {
+                      double *__restrict__ partials, size_t M, size_t N, size_t rows_per_chunk,
+                      double *__restrict__ direct_out, bool direct_accumulate) {
   constexpr int TY = 256 / TX;
   __shared__ double sm[TY][TX * VEC + 1];
   const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
@@ -263,7 +264,13 @@ colsum_partial_kernel(const double *__restrict__ g, double *__restrict__ gx, boo
     for (int l = 0; l < VEC; l++) {
       double t = 0.0;
       for (int y = 0; y < TY; y++) t += sm[y][tx * VEC + l];
-      partials[(size_t)blockIdx.y * N + cv * VEC + l] = t;
+      if (direct_out) {
+        // A single row chunk: this is already the column sum; no second stage.
+        double *dst = direct_out + cv * VEC + l;
+        *dst = direct_accumulate ? *dst + t : t;
+      } else {
+        partials[(size_t)blockIdx.y * N + cv * VEC + l] = t;
+      }
     }
   }
 }
@@ -465,18 +472,23 @@ int mg_add_row_bwd(const double *g, double *gx, double *grow, size_t M, size_t N
   if (rc != MG_OK) return rc;
   dim3 grid((unsigned)gridx, (unsigned)S);
   const bool gx_acc = !(flags & MG_ACC_STORE_A);
+  // One row chunk (few rows: the small-batch steps): the first stage writes the
+  // result itself, the same value the second stage would produce from one partial.
+  double *direct = S == 1 ? grow : nullptr;
+  const bool direct_acc = !(flags & MG_ACC_STORE_B);
   if (vec) {
     if (TX == 32)
-      colsum_partial_kernel<2, 32><<<grid, 256, 0, c.stream>>>(g, gx, gx_acc, c.colsum_scratch, M, N, rows_per_chunk);
+      colsum_partial_kernel<2, 32><<<grid, 256, 0, c.stream>>>(g, gx, gx_acc, c.colsum_scratch, M, N, rows_per_chunk, direct, direct_acc);
     else
-      colsum_partial_kernel<2, 8><<<grid, 256, 0, c.stream>>>(g, gx, gx_acc, c.colsum_scratch, M, N, rows_per_chunk);
+      colsum_partial_kernel<2, 8><<<grid, 256, 0, c.stream>>>(g, gx, gx_acc, c.colsum_scratch, M, N, rows_per_chunk, direct, direct_acc);
   } else {
     if (TX == 32)
-      colsum_partial_kernel<1, 32><<<grid, 256, 0, c.stream>>>(g, gx, gx_acc, c.colsum_scratch, M, N, rows_per_chunk);
+      colsum_partial_kernel<1, 32><<<grid, 256, 0, c.stream>>>(g, gx, gx_acc, c.colsum_scratch, M, N, rows_per_chunk, direct, direct_acc);
     else
-      colsum_partial_kernel<1, 8><<<grid, 256, 0, c.stream>>>(g, gx, gx_acc, c.colsum_scratch, M, N, rows_per_chunk);
+      colsum_partial_kernel<1, 8><<<grid, 256, 0, c.stream>>>(g, gx, gx_acc, c.colsum_scratch, M, N, rows_per_chunk, direct, direct_acc);
   }
   MG_LAUNCH_CHECK("colsum_partial");
+  if (direct) return MG_OK;
   colsum_finish_kernel<<<(unsigned)((N * 32 + 255) / 256), 256, 0, c.stream>>>(
       c.colsum_scratch, S, N, grow, !(flags & MG_ACC_STORE_B));
   MG_LAUNCH_CHECK("colsum_finish");
@@ -620,14 +632,14 @@ extern "C" int mg_colsum_noalloc(const double *g, double *out_row, size_t M, siz
   dim3 grid((unsigned)gridx, (unsigned)S);
   if (vec) {
     if (TX == 32)
-      colsum_partial_kernel<2, 32><<<grid, 256, 0, c.stream>>>(g, nullptr, false, scratch, M, N, rows_per_chunk);
+      colsum_partial_kernel<2, 32><<<grid, 256, 0, c.stream>>>(g, nullptr, false, scratch, M, N, rows_per_chunk, nullptr, false);
     else
-      colsum_partial_kernel<2, 8><<<grid, 256, 0, c.stream>>>(g, nullptr, false, scratch, M, N, rows_per_chunk);
+      colsum_partial_kernel<2, 8><<<grid, 256, 0, c.stream>>>(g, nullptr, false, scratch, M, N, rows_per_chunk, nullptr, false);
   } else {
     if (TX == 32)
-      colsum_partial_kernel<1, 32><<<grid, 256, 0, c.stream>>>(g, nullptr, false, scratch, M, N, rows_per_chunk);
+      colsum_partial_kernel<1, 32><<<grid, 256, 0, c.stream>>>(g, nullptr, false, scratch, M, N, rows_per_chunk, nullptr, false);
     else
-      colsum_partial_kernel<1, 8><<<grid, 256, 0, c.stream>>>(g, nullptr, false, scratch, M, N, rows_per_chunk);
+      colsum_partial_kernel<1, 8><<<grid, 256, 0, c.stream>>>(g, nullptr, false, scratch, M, N, rows_per_chunk, nullptr, false);
   }
   MG_LAUNCH_CHECK("colsum_partial (static scratch)");
   colsum_finish_kernel<<<(unsigned)((N * 32 + 255) / 256), 256, 0, c.stream>>>(scratch, S, N, out_row,
