@@ -42,6 +42,8 @@ def check_allreduce(abi, rank, world):
     for _ in range(3):                       # repeated calls reuse the flags
         for off, cnt in ranges:
             abi.mg_allreduce_sum_async(shared.value + 8 * off, cnt)
+    for off, cnt in ranges:                  # a fourth round with the wide ("exposed") grid
+        abi.mg_allreduce_sum_async_hint(shared.value + 8 * off, cnt, 1)
     for off, cnt in ranges:
         abi.mg_allreduce_sum_async(plain.ptr + 8 * off, cnt)   # not a shared buffer: NCCL
     abi.mg_comm_join()
@@ -61,16 +63,19 @@ def check_allreduce(abi, rank, world):
         thrice = twice.copy()
         for _ in range(world - 1):
             thrice = thrice + twice
+        fourth = thrice.copy()
+        for _ in range(world - 1):
+            fourth = fourth + thrice
         # NCCL adds the ranks' values in its own order: equal up to rounding of O(1) sums
         checks = [("nccl", np.allclose(nccl[off:off + cnt], once, rtol=0, atol=1e-13))]
         if peer:
-            checks.append(("peer (bit-exact)", np.array_equal(got[off:off + cnt], thrice)))
+            checks.append(("peer (bit-exact)", np.array_equal(got[off:off + cnt], fourth)))
         else:
-            checks.append(("fallback", np.allclose(got[off:off + cnt], thrice, rtol=0, atol=1e-11)))
+            checks.append(("fallback", np.allclose(got[off:off + cnt], fourth, rtol=0, atol=1e-10)))
         for what, passed in checks:
             if not passed:
                 ok = False
-                ref_v = once if what == "nccl" else thrice
+                ref_v = once if what == "nccl" else fourth
                 got_v = nccl[off:off + cnt] if what == "nccl" else got[off:off + cnt]
                 print(f"rank {rank}: {what} mismatch on range ({off}, {cnt}): "
                       f"max abs diff {np.abs(got_v - ref_v).max():.3e}", flush=True)
