@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(kPeerThreads) peer_allreduce_kernel(PeerArgs a
   __syncthreads();
   unsigned *mine = a.flags[a.rank];
 
-  // Round 1: tell every rank that this rank's inputs are final (they were written
+  // Flag phase 1: tell every rank that this rank's inputs are final (they were written
   // by kernels that completed before this one started), then wait for theirs.
   if (blockIdx.x == 0 && tid < W) {
     __threadfence_system();
@@ -239,7 +239,7 @@ __global__ void __launch_bounds__(kPeerThreads) peer_allreduce_kernel(PeerArgs a
     }
   }
 
-  // Round 2: once every CTA of this rank has pushed its results, tell every rank,
+  // Flag phase 2: once every CTA of this rank has pushed its results, tell every rank,
   // and have the last CTA stay until all ranks have said the same — when this
   // kernel completes, the whole reduced message is in this rank's buffer.
   __threadfence_system();
