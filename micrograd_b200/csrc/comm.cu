@@ -259,10 +259,16 @@ __global__ void __launch_bounds__(kPeerThreads) peer_allreduce_kernel(PeerArgs a
   }
 }
 
+// CTAs of an exchange that overlaps GEMMs.  A 512-thread CTA cannot share an SM
+// with a GEMM CTA, so every CTA here is an SM the GEMMs lose for as long as the
+// exchange is in flight (mostly waiting for the slowest peer).  Measured at 4 GPUs,
+// whole training step: 16 CTAs 4.99 ms (median 5.03), 8 CTAs 4.95, 4 CTAs 4.92
+// (median 4.92), 2 CTAs 4.92.  The one exchange nothing overlaps asks for a wide
+// grid instead (the `exposed` hint).
 int peer_ctas() {
   static const int v = [] {
     const char *e = std::getenv("MG_PEER_CTAS");
-    int n = e && *e ? std::atoi(e) : 16;
+    int n = e && *e ? std::atoi(e) : 4;
     const int sms = ctx().sm_count > 0 ? ctx().sm_count : 1;
     return n < 1 ? 1 : (n > sms ? sms : n);
   }();
