@@ -21,6 +21,13 @@
  *     first call that needs the device initialises it from MG_DEVICE, else
  *     LOCAL_RANK, else device 0.  There is no CPU fallback: without a usable
  *     CUDA device every call fails with MG_ERR_CUDA.
+ *   - One context per process, as the reference keeps one MetalContext
+ *     (src/metal/MetalContext.cpp:9-12).  Initialisation and shutdown are
+ *     guarded by a lock; everything else (the launch counter, the scratch
+ *     buffers, the cache of GEMM segment tables, the recording state) is not,
+ *     so calls from several host threads must not overlap: the reference's
+ *     Tensor code is single-threaded and so is the layer above this header.
+ *     Several GPUs are driven by several processes, never by threads.
  *   - Backward entry points ACCUMULATE (`+=`), like the reference's closures.
  *     `flags` bit MG_ACC_STORE_A / _B says the destination gradient is known to
  *     be all zero, so the kernel may store instead of read-modify-write; the
