@@ -4,7 +4,9 @@ Each rank takes its row shard of a global batch, computes its gradients with the
 CPU oracle using the GLOBAL batch size as the loss divisor (what each GPU rank
 does), the shards' gradients are summed with a gloo all-reduce (standing in for
 the library's NCCL all-reduce), and the result must equal the single-process
-full-batch gradients.  Also covers the byte broadcast that ships the NCCL id.
+full-batch gradients.  Also covers the byte broadcast that ships the NCCL id, and the row-sharded
+inference pass (no exchange; class ids and their checksum equal the
+single-process ones).
 """
 import os
 import socket
@@ -80,3 +82,47 @@ def test_two_rank_sharded_gradients_equal_full_batch(tmp_path):
         assert abs(got["loss"][0] - loss) <= 1e-13 * abs(loss)
         assert bytes(got["uid"]) == bytes(range(128))
         assert float(got["slowest"]) == float(world)
+
+
+def _inference_worker(rank, world, port, out_dir, rows):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import bench
+    import oracle
+    fast = oracle.fast
+    fast.set_num_threads(1)
+    params = _inference_params()
+    b, e = shard_rows(rows, rank, world)
+    # every rank generates only its own rows of the one global input stream
+    X = bench.uniform01_host(77, b * 20, (e - b) * 20).reshape(e - b, 20)
+    logits, _ = fast.mlp_forward(params, X)
+    ids = fast.argmax_rows(logits)
+    part = torch.tensor([bench.ids_checksum(ids, b)], dtype=torch.int64)
+    dist.all_reduce(part)                                   # the only cross-rank step: a checksum
+    np.savez(os.path.join(out_dir, f"inf{rank}.npz"), ids=ids, checksum=part.numpy(), span=[b, e])
+    dist.destroy_process_group()
+
+
+def _inference_params():
+    rng = np.random.default_rng(5)
+    sizes = [20, 16, 12, 10]
+    return [(rng.standard_normal((i, o)) / np.sqrt(i), 0.1 * rng.standard_normal(o))
+            for i, o in zip(sizes[:-1], sizes[1:])]
+
+
+def test_two_rank_sharded_inference_gives_the_same_class_ids(tmp_path):
+    """Inference shards rows with no exchange: the ranks' class ids, put side by
+    side, are the single-process ids, and the summed checksums agree."""
+    import bench
+    import oracle
+    world, rows = 2, 1001                                   # odd: the shards differ in length
+    mp.spawn(_inference_worker, args=(world, _free_port(), str(tmp_path), rows), nprocs=world, join=True)
+    X = bench.uniform01_host(77, 0, rows * 20).reshape(rows, 20)
+    logits, _ = oracle.fast.mlp_forward(_inference_params(), X)
+    want = oracle.fast.argmax_rows(logits)
+    got = [np.load(tmp_path / f"inf{r}.npz") for r in range(world)]
+    assert [tuple(g["span"]) for g in got] == [(0, 501), (501, 1001)]
+    assert np.array_equal(np.concatenate([g["ids"] for g in got]), want)
+    assert len(set(want.tolist())) > 1                      # not a degenerate classifier
+    for g in got:
+        assert int(g["checksum"][0]) == bench.ids_checksum(want, 0)
