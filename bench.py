@@ -620,7 +620,7 @@ def small_batch_leg(abi, api):
            "us_per_step": dev_ms * 1e3 / n, "us_per_step_host_wall": wall_ms * 1e3 / n,
            "samples_per_s": 32 * n / (dev_ms * 1e-3), "launches_per_step": launches,
            "frac_of_nominal_fp64": flop / (dev_ms * 1e-3 / n) / 1e12 / NOMINAL_FP64_TFLOPS,
-           "bound": "kernel-launch latency (a chain of ~20 dependent micro-kernels)"}
+           "bound": "kernel-launch latency (a chain of dependent micro-kernels, see launches_per_step)"}
     # The same step recorded once (CUDA graph) and replayed with one launch per step.
     del loss
     rec = api.RecordedStep()
