@@ -381,6 +381,47 @@ argmax_rows_kernel(const double *__restrict__ x, int *__restrict__ out, size_t M
   }
 }
 
+// Narrow rows (N <= kNarrowCols, the ten logits of a classifier): a warp per row
+// leaves most lanes idle and serialises on one dependent load per row.  Here a CTA
+// takes kNarrowRows consecutive rows — one contiguous range of the matrix — copies
+// it to shared memory with coalesced loads, and every thread then walks one row left
+// to right exactly as the reference's loop does (src/main.cpp:29-32: `>` against the
+// best so far, so ties keep the lower index and a NaN never replaces anything).
+constexpr int kNarrowRows = 128;
+constexpr int kNarrowCols = 32;
+
+__global__ void __launch_bounds__(kNarrowRows)
+argmax_narrow_rows_kernel(const double *__restrict__ x, int *__restrict__ out, size_t M, int N) {
+  __shared__ double tile[kNarrowRows * (kNarrowCols + 1)];
+  const int stride = N | 1;  // odd row pitch: the column walk spreads over the banks
+  const size_t tiles = (M + kNarrowRows - 1) / kNarrowRows;
+  for (size_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+    const size_t row0 = t * kNarrowRows;
+    const int rows = (int)(M - row0 < (size_t)kNarrowRows ? M - row0 : (size_t)kNarrowRows);
+    const double *src = x + row0 * (size_t)N;
+    const int count = rows * N;
+    for (int i = threadIdx.x; i < count; i += kNarrowRows) {
+      const int r = i / N;
+      tile[r * stride + (i - r * N)] = src[i];
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < rows) {
+      const double *r = tile + threadIdx.x * stride;
+      double best = r[0];
+      int best_j = 0;
+      for (int j = 1; j < N; j++) {
+        const double v = r[j];
+        if (v > best) {
+          best = v;
+          best_j = j;
+        }
+      }
+      out[row0 + threadIdx.x] = best_j;
+    }
+    __syncthreads();
+  }
+}
+
 static unsigned sum_grid(size_t vectors) {
   // Enough CTAs that each thread has a few vectors, never more than kSumCtas.
   size_t need = (vectors + (size_t)kSumThreads * 4 - 1) / ((size_t)kSumThreads * 4);
@@ -531,7 +572,14 @@ int mg_argmax_rows(const double *x, int *out, size_t M, size_t N) {
   if (!x || !out) return fail(MG_ERR_INVALID, "mg_argmax_rows: null pointer");
   if (N == 0) return fail(MG_ERR_INVALID, "mg_argmax_rows: rows are empty");
   Context &c = ctx();
-  argmax_rows_kernel<<<grid_for(M * 32, 256, 8), 256, 0, c.stream>>>(x, out, M, N);
+  if (N <= (size_t)kNarrowCols) {
+    const size_t tiles = (M + kNarrowRows - 1) / kNarrowRows;
+    const size_t cap = (size_t)c.sm_count * 24;  // six resident CTAs per SM, four waves
+    argmax_narrow_rows_kernel<<<(unsigned)(tiles < cap ? tiles : cap), kNarrowRows, 0, c.stream>>>(
+        x, out, M, (int)N);
+  } else {
+    argmax_rows_kernel<<<grid_for(M * 32, 256, 8), 256, 0, c.stream>>>(x, out, M, N);
+  }
   MG_LAUNCH_CHECK("argmax_rows");
   return MG_OK;
 }

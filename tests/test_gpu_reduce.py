@@ -136,7 +136,9 @@ def test_softmax_cross_entropy_flags_bad_label(abi):
     abi.mg_check_kernel_status()  # the fault word is cleared once reported
 
 
-@pytest.mark.parametrize("M,N", [(1, 1), (5, 3), (1000, 10), (65536, 10), (33, 100)])
+@pytest.mark.parametrize("M,N", [(1, 1), (5, 3), (1000, 10), (65536, 10), (33, 100), (127, 10), (128, 10),
+                                 (129, 10), (300, 31), (1000, 32), (1000, 33), (7, 16), (100003, 7),
+                                 (1 << 20, 10)])
 def test_argmax_rows_bit_exact(abi, fast, M, N):
     rng = np.random.default_rng(M + N)
     x = rng.standard_normal((M, N))
@@ -144,6 +146,30 @@ def test_argmax_rows_bit_exact(abi, fast, M, N):
     dx, out = abi.array(x), abi.int_array(np.zeros(M, dtype=np.int32))
     abi.mg_argmax_rows(dx.ptr, out.ptr, M, N)
     assert np.array_equal(out.numpy(), fast.argmax_rows(x))
+
+
+def test_argmax_of_narrow_rows_follows_the_reference_loop_on_special_values(abi, fast):
+    """Rows of at most 32 columns are walked left to right with `>` like the
+    reference's prediction loop: ties and -0.0/+0.0 keep the lower index, a NaN
+    never replaces the best so far, and a leading NaN is never replaced."""
+    nan, inf = np.nan, np.inf
+    rows = np.array([
+        [0.0, -0.0, 0.0, -0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0],
+        [-0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0],
+        [nan, 1.0, 2.0, 3.0, 4.0, 5.0, 6.0, 7.0, 8.0, 9.0],
+        [1.0, nan, 2.0, nan, 2.0, 0.0, 0.0, 0.0, 0.0, 0.0],
+        [-inf, -inf, -inf, -inf, -inf, -inf, -inf, -inf, -inf, -inf],
+        [-inf, -1e308, -inf, -1e308, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0],
+        [1.0, 2.0, inf, inf, 3.0, 0.0, 0.0, 0.0, 0.0, 0.0],
+        [5e-324, 0.0, 5e-324, 1e-323, 1e-323, 0.0, 0.0, 0.0, 0.0, 0.0],
+        [3.0, 3.0, 3.0, 3.0, 3.0, 3.0, 3.0, 3.0, 3.0, np.nextafter(3.0, 4.0)],
+    ])
+    x = np.tile(rows, (40, 1))                        # 360 rows: three CTAs, a ragged last one
+    want = fast.argmax_rows(x)
+    assert list(want[:9]) == [0, 0, 0, 2, 0, 4, 2, 3, 9]
+    dx, out = abi.array(x), abi.int_array(np.zeros(x.shape[0], dtype=np.int32))
+    abi.mg_argmax_rows(dx.ptr, out.ptr, x.shape[0], 10)
+    assert np.array_equal(out.numpy(), want)
 
 
 def test_label_conversion(abi):
