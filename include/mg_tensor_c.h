@@ -109,6 +109,7 @@ int mgt_comm_shutdown(void);
 int mgt_sgd_enable_allreduce(mgt_sgd s);
 /* Tensor::copy_from_host and micrograd::RecordedStep (one recorded step per process here). */
 int mgt_copy_from_host(mgt_tensor t, const double *values, size_t n);
+int mgt_prefetch_from_host(mgt_tensor t, const double *values, size_t n); /* Tensor::prefetch_from_host */
 int mgt_record_begin(void);
 int mgt_record_end(void);
 int mgt_record_replay(void);

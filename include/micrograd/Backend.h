@@ -18,6 +18,13 @@ enum class Backend { CPU, Metal, CUDA };
 // Blocks until all device work enqueued so far has finished.
 void synchronize();
 
+// Makes sure the device memory pool behind every tensor holds `bytes` that no
+// tensor is using.  Tensors are allocated and freed every step; when the pool has
+// to grow while kernels are running the calling thread stalls (tens to hundreds
+// of milliseconds in a multi-GPU job).  Call once before a loop that must not
+// stall, with the loop's peak footprint plus slack.
+void reserve_device_memory(std::size_t bytes);
+
 // A launch-bound step — the reference trainer's per-sample loop
 // (src/main.cpp:20-46) enqueues about twenty dependent micro-kernels per sample —
 // recorded once and replayed with a single launch (a CUDA graph):

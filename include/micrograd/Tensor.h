@@ -85,6 +85,14 @@ public:
   // device buffer (and its address) the tensor already has: how the input of a
   // recorded step is refreshed.
   void copy_from_host(const double *values);
+  // The same, but the copy runs on the library's copy stream: it starts when the
+  // kernels enqueued so far have finished (they may still read the old values),
+  // overlaps whatever is enqueued afterwards, and the next operation that uses
+  // this tensor waits for it.  With two input tensors refreshed in turn, the batch
+  // of step i+1 uploads while step i computes and nothing is allocated per step.
+  // `values` must stay unchanged until that next use has completed (pinned memory
+  // for a copy that really overlaps).  Not for the input of a recorded step.
+  void prefetch_from_host(const double *values);
   // Read-only host views.  Unlike the mutable data()/grad() of the reference
   // interface they do not hand out a writable reference, so the device copy stays
   // current and no re-upload follows the read.

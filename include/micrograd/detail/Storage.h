@@ -60,6 +60,7 @@ public:
   // buffer this storage already has (its address does not change, which a recorded
   // step relies on).
   void upload_in_place(const double *values);
+  void prefetch_in_place(const double *values);  // the same through the copy stream
 
   // Moves the contents into caller-owned device memory (a slice of a flat
   // parameter/gradient buffer) and uses that memory from now on.

@@ -38,6 +38,7 @@ SIGNATURES = {
     "mg_kernel_status_mirror": (C.c_int, []),
     "mg_kernel_status_peek": (C.c_int, [_ip]),
     "mg_mem_info": (C.c_int, [C.POINTER(_sz), C.POINTER(_sz)]),
+    "mg_pool_reserve": (C.c_int, [_sz]),
     "mg_alloc": (C.c_int, [_sz, C.POINTER(C.c_void_p)]),
     "mg_free": (C.c_int, [C.c_void_p]),
     "mg_alloc_i32": (C.c_int, [_sz, C.POINTER(C.c_void_p)]),

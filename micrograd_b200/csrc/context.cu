@@ -282,6 +282,18 @@ int mg_free(double *p) {
 
 int mg_free_i32(int *p) { return mg_free(reinterpret_cast<double *>(p)); }
 
+int mg_pool_reserve(size_t bytes) {
+  MG_ENSURE_INIT();
+  MG_NOT_WHILE_RECORDING("mg_pool_reserve");
+  if (bytes == 0) return MG_OK;
+  // One block of the whole size: if the pool already has such a hole this costs
+  // nothing, otherwise the pool grows now rather than in the caller's loop.
+  void *block = nullptr;
+  int rc = alloc_bytes(bytes, &block);
+  if (rc != MG_OK) return rc;
+  return mg_free(static_cast<double *>(block));
+}
+
 int mg_upload(double *dst, const double *src_host, size_t n) {
   MG_ENSURE_INIT();
   MG_NOT_WHILE_RECORDING("mg_upload (the host address would be baked into the graph)");

@@ -9,6 +9,8 @@ using detail::check;
 
 void synchronize() { check(mg_sync(), "synchronize"); }
 
+void reserve_device_memory(std::size_t bytes) { check(mg_pool_reserve(bytes), "reserve_device_memory"); }
+
 RecordedStep::~RecordedStep() {
   if (recording_) {
     // Abandoned between begin() and end(): close the recording so that later work

@@ -411,6 +411,15 @@ int mgt_copy_from_host(mgt_tensor t, const double *values, size_t n) {
   });
 }
 
+int mgt_prefetch_from_host(mgt_tensor t, const double *values, size_t n) {
+  return guard_int([&] {
+    if (n != t->p->size()) {
+      throw std::invalid_argument("mgt_prefetch_from_host: size mismatch");
+    }
+    t->p->prefetch_from_host(values);
+  });
+}
+
 namespace {
 // The one recorded step this flat binding offers; replaced by a fresh object when
 // the caller abandons it.

@@ -258,6 +258,19 @@ void Storage::upload_in_place(const double *values) {
   host_valid_ = false;
 }
 
+void Storage::prefetch_in_place(const double *values) {
+  write_stamp_++;
+  settle_upload();  // an earlier prefetch into the same buffer is ordered first
+  ensure_device_buffer();
+  // The copy stream waits for everything enqueued on the compute stream so far
+  // (every earlier reader of this buffer), copies, and the next kernel that
+  // touches the buffer waits for the copy (settle_upload).
+  check(mg_upload_async(dev_, values, size_, &pending_upload_), "upload");
+  zero_ = false;
+  dev_valid_ = true;
+  host_valid_ = false;
+}
+
 void Storage::rehome(double *slice, std::shared_ptr<void> keepalive) {
   settle_upload();
   if (!zero_) {

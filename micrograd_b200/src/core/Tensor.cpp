@@ -83,6 +83,8 @@ std::vector<double> &Tensor::grad() { return grad_.host_mutable(); }
 
 void Tensor::copy_from_host(const double *values) { data_.upload_in_place(values); }
 
+void Tensor::prefetch_from_host(const double *values) { data_.prefetch_in_place(values); }
+
 const std::vector<double> &Tensor::data() const { return data_.host_const(); }
 
 const std::vector<double> &Tensor::grad() const { return grad_.host_const(); }

@@ -90,6 +90,7 @@ def _declare(lib, extensions: bool) -> None:
             "mgt_comm_shutdown": (C.c_int, []),
             "mgt_sgd_enable_allreduce": (C.c_int, [vp]),
             "mgt_copy_from_host": (C.c_int, [vp, _c_double_p, C.c_size_t]),
+            "mgt_prefetch_from_host": (C.c_int, [vp, C.c_void_p, C.c_size_t]),
             "mgt_record_begin": (C.c_int, []),
             "mgt_record_end": (C.c_int, []),
             "mgt_record_replay": (C.c_int, []),
@@ -243,6 +244,11 @@ def bind(path: str) -> SimpleNamespace:
             """Tensor::copy_from_host: new values into the device buffer the tensor has."""
             arr = _as_f64(values)
             _check(lib.mgt_copy_from_host(self._h, arr.ctypes.data_as(_c_double_p), arr.size))
+
+        def prefetch_from_host(self, pointer: int) -> None:
+            """Tensor::prefetch_from_host: size() doubles from a raw host address (e.g.
+            pinned memory) into the buffer the tensor has, on the copy stream."""
+            _check(lib.mgt_prefetch_from_host(self._h, C.c_void_p(pointer), self.size()))
 
     class Linear:
         """Mirror of ``class Linear`` (reference include/micrograd/nn.h:10-21)."""
