@@ -8,6 +8,7 @@
 #include <fstream>
 #include <memory>
 #include <stdexcept>
+#include <utility>
 #include <vector>
 
 #include "mg_cuda.h"
@@ -120,6 +121,31 @@ TEST(ApiTest, IntermediatesAreFreed) {
   ASSERT_EQ(mg_mem_info(&free_after, &total), 0);
   // 50 iterations x 4 intermediates x (8 + 8) MiB would be 3.2 GB if leaked.
   EXPECT_LT(free_before - std::min(free_before, free_after), static_cast<size_t>(256) << 20);
+}
+
+// Two inputs refreshed in turn on the copy stream: each result belongs to the
+// batch that was current when its step was built, and a host read sees the new values.
+TEST(ApiTest, PrefetchFromHostRefreshesInPlace) {
+  micrograd::reserve_device_memory(static_cast<size_t>(64) << 20);
+  const size_t n = 1 << 16;
+  std::vector<std::vector<double>> batches(4, std::vector<double>(n));
+  for (size_t b = 0; b < batches.size(); b++) {
+    for (size_t i = 0; i < n; i++) batches[b][i] = static_cast<double>((i % 7) + b);
+  }
+  std::shared_ptr<Tensor> x[2] = {Tensor::from_host({n}, batches[0].data()),
+                                  Tensor::from_host({n}, batches[1].data())};
+  std::vector<std::shared_ptr<Tensor>> sums;
+  for (size_t b = 0; b < batches.size(); b++) {
+    if (b >= 2) x[b % 2]->prefetch_from_host(batches[b].data());
+    sums.push_back(x[b % 2]->mul(2.0)->sum());
+  }
+  for (size_t b = 0; b < batches.size(); b++) {
+    double want = 0.0;
+    for (double v : batches[b]) want += 2.0 * v;
+    EXPECT_DOUBLE_EQ(std::as_const(*sums[b]).data()[0], want);  // small integers: exact in any order
+  }
+  EXPECT_EQ(std::as_const(*x[1]).data()[5], batches[3][5]);
+  EXPECT_EQ(std::as_const(*x[0]).data()[n - 1], batches[2][n - 1]);
 }
 
 TEST(ApiTest, ToDotMentionsOps) {
