@@ -21,6 +21,25 @@ struct RecordedStep {
   unsigned long long kernels = 0;  // kernel nodes, for the launch counter
 };
 std::vector<RecordedStep> g_steps;
+// Scratch buffers that were outgrown while a recorded step existed: the step's
+// kernels carry the old address, so the memory stays allocated until shutdown.
+std::vector<void *> g_retired_scratch;
+
+bool any_recorded_step() {
+  for (const auto &step : g_steps)
+    if (step.exec) return true;
+  return false;
+}
+
+// Gives up an outgrown scratch buffer (stream-ordered free, or parked, see above).
+cudaError_t retire_scratch(void *buf, cudaStream_t stream) {
+  if (!buf) return cudaSuccess;
+  if (any_recorded_step()) {
+    g_retired_scratch.push_back(buf);
+    return cudaSuccess;
+  }
+  return cudaFreeAsync(buf, stream);
+}
 }  // namespace
 
 Context &ctx() { return g_ctx; }
@@ -112,7 +131,7 @@ int ensure_scratch(double **buf, size_t *have, size_t elems) {
     return fail(MG_ERR_INVALID,
                 "a scratch buffer would have to grow while a step is being recorded; run the step "
                 "once before mg_graph_begin()");
-  if (*buf) MG_CUDA_TRY(cudaFreeAsync(*buf, c.stream));
+  MG_CUDA_TRY(retire_scratch(*buf, c.stream));
   *buf = nullptr;
   *have = 0;
   MG_CUDA_TRY(cudaMallocAsync(buf, elems * sizeof(double), c.stream));
@@ -163,6 +182,8 @@ int mg_shutdown(void) {
     if (step.exec) cudaGraphExecDestroy(step.exec);
   g_steps.clear();
   release_mirror_ring_at_shutdown();
+  for (void *buf : g_retired_scratch) cudaFreeAsync(buf, c.stream);
+  g_retired_scratch.clear();
   if (c.colsum_scratch) cudaFreeAsync(c.colsum_scratch, c.stream);
   if (c.splitk_scratch) cudaFreeAsync(c.splitk_scratch, c.stream);
   cudaStreamSynchronize(c.stream);

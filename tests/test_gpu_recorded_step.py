@@ -152,3 +152,45 @@ def test_abandoned_recording_is_closed(api, abi):
     del pending
     assert a.mul(3.0).sum().data()[0] == 30.0  # executes
     abi.mg_check_kernel_status()
+
+
+def test_replay_survives_scratch_buffers_outgrown_after_the_recording(api, abi):
+    """A recorded bias-gradient column sum carries the address of the library's
+    scratch buffer for partial sums.  A larger column sum after the recording makes
+    the library take a bigger buffer; the old one must stay alive for the replay,
+    which is checked here with fresh allocations in between that would otherwise
+    land on the freed memory."""
+    rng = np.random.default_rng(3)
+    rows, cols = 4096, 256                        # several row chunks: partials + second stage
+    X = rng.standard_normal((rows, cols))
+    x = api.Tensor([rows, cols], X)
+    bias = api.Tensor([1, cols], np.zeros((1, cols)))
+
+    def bias_grad():
+        bias.zero_grad()
+        out = x.add(bias).sum()                   # row-broadcast add; backward = column sum of ones
+        out.backward()
+        return out
+
+    first = bias_grad()                           # normal run: scratch buffers get their first size
+    want = np.array(bias.grad()).copy()
+    assert np.array_equal(want, np.full(cols, float(rows)))
+    del first
+    rec = api.RecordedStep()
+    rec.begin()
+    out = bias_grad()
+    rec.end()
+    # outgrow the scratch buffer (wider and taller), then churn the pool
+    wide = api.Tensor([8192, 4096], np.ones((8192, 4096)))
+    wide_bias = api.Tensor([1, 4096], np.zeros((1, 4096)))
+    wide.add(wide_bias).sum().backward()
+    assert np.array_equal(np.array(wide_bias.grad()), np.full(4096, 8192.0))
+    junk = [api.Tensor([1 << 16], np.full(1 << 16, 7.0)) for _ in range(32)]
+    for t in junk:
+        t.mul(2.0)
+    for _ in range(3):
+        rec.replay()
+        assert np.array_equal(np.array(bias.grad()), want)
+        assert abs(out.data()[0] - X.sum()) <= 1e-10 * np.abs(X).sum()
+    abi.mg_check_kernel_status()
+    del junk
