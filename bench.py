@@ -35,6 +35,7 @@ from __future__ import annotations
 
 import argparse
 import ctypes as C
+import gc
 import json
 import os
 import subprocess
@@ -405,12 +406,18 @@ def run_product(args):
 
     e2e_marks = []
     x_next = e2e_loop(3, upload())
+    # As timeit does: no garbage-collector pass inside the host-timed region (the
+    # loop makes a few hundred short-lived wrapper objects per step, and a full
+    # collection over an interpreter with torch loaded takes milliseconds).
+    gc.collect()
+    gc.disable()
     barrier()
     e2e_marks.clear()
     t0 = time.perf_counter()
     x_next = e2e_loop(e2e_steps, x_next)
     abi.mg_sync()
     e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3)
+    gc.enable()
     # host time between consecutive loss reads on this rank (rank 0's view in the line)
     e2e_gaps = np.diff(np.array([t0] + e2e_marks)) * 1e3
     if os.environ.get("MG_E2E_DIAG"):
