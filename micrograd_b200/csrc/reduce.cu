@@ -392,8 +392,8 @@ constexpr int kNarrowCols = 32;
 
 __global__ void __launch_bounds__(kNarrowRows)
 argmax_narrow_rows_kernel(const double *__restrict__ x, int *__restrict__ out, size_t M, int N) {
-  __shared__ double tile[kNarrowRows * (kNarrowCols + 1)];
-  const int stride = N | 1;  // odd row pitch: the column walk spreads over the banks
+  extern __shared__ double tile[];  // kNarrowRows x stride doubles, sized by the launch
+  const int stride = N | 1;         // odd row pitch: the column walk spreads over the banks
   const size_t tiles = (M + kNarrowRows - 1) / kNarrowRows;
   for (size_t t = blockIdx.x; t < tiles; t += gridDim.x) {
     const size_t row0 = t * kNarrowRows;
@@ -574,9 +574,12 @@ int mg_argmax_rows(const double *x, int *out, size_t M, size_t N) {
   Context &c = ctx();
   if (N <= (size_t)kNarrowCols) {
     const size_t tiles = (M + kNarrowRows - 1) / kNarrowRows;
-    const size_t cap = (size_t)c.sm_count * 24;  // six resident CTAs per SM, four waves
-    argmax_narrow_rows_kernel<<<(unsigned)(tiles < cap ? tiles : cap), kNarrowRows, 0, c.stream>>>(
-        x, out, M, (int)N);
+    // The tile is sized by the actual column count (11 KB for ten columns, 34 KB at
+    // most), so shared memory does not cap residency; about four waves of CTAs.
+    const size_t tile_bytes = (size_t)kNarrowRows * (N | 1) * sizeof(double);
+    const size_t cap = (size_t)c.sm_count * 40;
+    argmax_narrow_rows_kernel<<<(unsigned)(tiles < cap ? tiles : cap), kNarrowRows, tile_bytes,
+                                c.stream>>>(x, out, M, (int)N);
   } else {
     argmax_rows_kernel<<<grid_for(M * 32, 256, 8), 256, 0, c.stream>>>(x, out, M, N);
   }
